@@ -1,0 +1,128 @@
+/* piper_b200.h — C ABI of libpiper_b200.so: fused quantized attention forward for NVIDIA B200
+ * (sm_100a).  Plain pointers and sizes only; no torch types.  All entry points are
+ * re-entrant, launch on the caller's stream of the caller's device, never allocate device
+ * memory and never synchronise (except pk_device_status, which the caller asks for).
+ *
+ * The library replaces, for this one path, the operators that the reference project
+ * (Boffee/piper-kernels) registers as
+ *   piper_kernels::piper_attention(query, key, value, scale, is_causal, center_value)
+ *       src/piper_kernels/attention/piper/triton.py:1319-1348
+ *   piper_kernels::sage_attention_2pp(query, key, value, scale, is_causal)
+ *       src/piper_kernels/attention/sage2pp/triton.py:434-443, 682-690
+ * and the host orchestration behind them (prepare, then launch):
+ *   _prepare_piper_attention / _launch_piper_attention   piper/triton.py:1054-1289
+ *   _run_sage_attention_2pp                               sage2pp/triton.py:446-679
+ */
+#ifndef PIPER_B200_H
+#define PIPER_B200_H
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define PK_ABI_VERSION 1
+
+#if defined(__GNUC__)
+#define PK_API __attribute__((visibility("default")))
+#else
+#define PK_API
+#endif
+
+/* return codes */
+#define PK_OK 0
+#define PK_ERR_BAD_ARG 1          /* shape / dtype / pointer / alignment rejected before launch */
+#define PK_ERR_UNSUPPORTED_ARCH 2 /* device is not compute capability 10.x */
+#define PK_ERR_WORKSPACE 3        /* workspace missing or smaller than pk_*_workspace_bytes */
+#define PK_ERR_CUDA 4             /* a CUDA runtime / driver call failed (message has details) */
+#define PK_ERR_DEVICE_STATUS 5    /* a kernel gave up a bounded wait; see pk_device_status */
+
+/* element types */
+#define PK_F16 0
+#define PK_BF16 1
+#define PK_F32 2 /* output only: un-rounded result for parity checks */
+
+/* Q/K scale granularity (reference: qk_quantization="per_warp" | "per_thread",
+ * attention/kernels/qk_quantization/int8/sage/reference.py:20-74) */
+#define PK_QK_PER_BLOCK 0  /* one scale per 32 query rows / 64 key rows */
+#define PK_QK_PER_THREAD 1 /* SageAttention's interleaved row groups */
+
+/* One attention call.  Tensors are [batch, heads, sequence, head_dim] with a contiguous head
+ * dimension; strides are in elements for batch, head and sequence.  q/k/v are borrowed and
+ * never written.  `out` is contiguous [batch, heads, q_len, head_dim]. */
+typedef struct pk_problem {
+  int32_t batch, heads, q_len, kv_len, head_dim; /* head_dim 64 or 128 */
+  int32_t in_dtype;                              /* PK_F16 | PK_BF16 */
+  int32_t out_dtype;                             /* in_dtype, or PK_F32 */
+  int32_t is_causal;                             /* requires q_len == kv_len */
+  int32_t center_value;                          /* piper: subtract the sequence mean of V */
+  int32_t sort_value_rows;                       /* piper: centred-row-range key order */
+  int32_t qk_granularity;                        /* PK_QK_PER_BLOCK | PK_QK_PER_THREAD */
+  float scale;                                   /* softmax scale, finite and > 0 */
+  const void* q;
+  const void* k;
+  const void* v;
+  int64_t q_stride[3], k_stride[3], v_stride[3]; /* batch, head, sequence (elements) */
+  void* out;
+  const float* k_mean_override; /* optional [batch*heads, head_dim] f32 device pointers:  */
+  const float* v_mean_override; /* use these means instead of computing them              */
+  void* workspace;              /* device scratch, 256-byte aligned                       */
+  uint64_t workspace_bytes;
+  int32_t device; /* CUDA device ordinal that owns every pointer */
+  void* stream;   /* cudaStream_t */
+} pk_problem;
+
+/* Device pointers into the workspace after a prepare call (for parity tests and for callers
+ * that re-use quantised K/V).  Shapes: BH = batch*heads, Sq_pad = q_len rounded up to 128,
+ * Sk_pad = kv_len rounded up to 64.  Padding rows hold zero codes. */
+typedef struct pk_views {
+  int8_t* q_codes;        /* [BH, Sq_pad, D]                                             */
+  int8_t* k_codes;        /* [BH, Sk_pad, D]  (rows in sorted order when sorting)        */
+  uint8_t* v_codes_t;     /* [BH, D, Sk_pad]  piper: int8; sage: E4M3                    */
+  float* q_group_scale;   /* per-block: [BH, ceil(q_len/32)]; per-thread: [BH, q_len]    */
+  float* k_group_scale;   /* per-block: [BH, ceil(kv_len/64)]; per-thread: [BH, kv_len]  */
+  float* v_scale;         /* piper: [BH, kv_len] per key; sage: [BH, D] per channel      */
+  float* k_mean;          /* [BH, D]                                                     */
+  float* v_mean;          /* [BH, D] (zeros when not centring; unused by sage)           */
+  int32_t* order;         /* [BH, kv_len] when sorting, else NULL                        */
+  float* q_row_mul;       /* [BH, Sq_pad] q scale * softmax scale * log2(e)              */
+  float* k_col_mul;       /* [BH, Sk_pad] per-key K scale                                */
+  float* k_col_add;       /* [BH, Sk_pad] piper: log2(v scale); sage: 0; padding: -inf   */
+  float* k_col_inv;       /* [BH, Sk_pad] piper: 1 / v scale; padding 0                  */
+  int32_t* status;        /* [16] device status words, zero when healthy                 */
+  int32_t sq_pad, sk_pad;
+} pk_views;
+
+PK_API int pk_version(void);
+/* Message of the last failing call on this thread ("" if none). */
+PK_API const char* pk_last_error(void);
+
+/* Piper attention.  Replaces _prepare_piper_attention + _launch_piper_attention
+ * (piper/triton.py:1054-1289) behind piper_kernels::piper_attention (:1319-1336). */
+PK_API int pk_piper_workspace_bytes(const pk_problem* p, uint64_t* bytes);
+PK_API int pk_piper_prepare(const pk_problem* p, pk_views* views); /* prepass only (piper/triton.py:1054-1236) */
+PK_API int pk_piper_run(const pk_problem* p);                      /* fused kernel on a prepared workspace (:1239-1289) */
+PK_API int pk_piper_attention_fwd(const pk_problem* p);            /* prepare + run */
+
+/* SageAttention2++ (8+8).  Replaces _run_sage_attention_2pp (sage2pp/triton.py:446-679)
+ * behind piper_kernels::sage_attention_2pp (:434-443). */
+PK_API int pk_sage2pp_workspace_bytes(const pk_problem* p, uint64_t* bytes);
+PK_API int pk_sage2pp_prepare(const pk_problem* p, pk_views* views);
+PK_API int pk_sage2pp_run(const pk_problem* p);
+PK_API int pk_sage2pp_attention_fwd(const pk_problem* p);
+
+/* Copies the 16 status words of the workspace to the host after synchronising the stream.
+ * status[0] != 0 means a kernel abandoned a wait (the value says which one). */
+PK_API int pk_device_status(const pk_problem* p, int32_t status[16]);
+
+/* Debug aid for parity tests: runs the fused kernel and also copies the raw INT32 score tile
+ * (first 64 keys, [128,64]), the packed probability codes ([128,64] bytes) and the raw PV
+ * partial ([128, head_dim], int32 for piper / f32 for sage) of query tile `q_tile` of flattened
+ * head `bh` into `dump` (device memory, 128*64*4 + 128*64 + 128*head_dim*4 bytes). */
+PK_API int pk_debug_first_tile(const pk_problem* p, int sage, int bh, int q_tile, void* dump);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* PIPER_B200_H */

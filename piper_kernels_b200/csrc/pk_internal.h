@@ -1,0 +1,52 @@
+// Internal declarations shared by the translation units of libpiper_b200.so.
+#pragma once
+
+#include <cuda_runtime.h>
+#include <stddef.h>
+#include <stdint.h>
+
+#include "../../include/piper_b200.h"
+
+namespace pk {
+
+constexpr int kQTile = 128;       // query rows per CTA of the fused kernel
+constexpr int kKeyTile = 64;      // keys per softmax tile (part of the numerics)
+constexpr int kStatChunkRows = 512;  // rows per partial column reduction
+constexpr float kLog2e = 1.4426950408889634f;
+
+enum Algo : int { kPiper = 0, kSage = 1 };
+
+// Byte offsets of every intermediate inside the caller's workspace.
+struct Layout {
+  int BH, D, Sq, Sk, sq_pad, sk_pad, chunks;
+  int q_groups, k_groups;  // entries per head of the group-scale arrays
+  size_t status, k_mean, v_mean, k_part, v_part, q_codes, k_codes, v_codes, q_gscale, k_gscale,
+      v_scale, q_mul, k_mul, k_add, k_inv, range, keys_alt, idx_a, idx_b, total;
+};
+
+Layout make_layout(const pk_problem& p, Algo algo);
+
+// Sets the thread-local error message and returns `code`.
+int fail(int code, const char* fmt, ...);
+const char* cuda_err(cudaError_t e);
+
+// Argument checks shared by every entry point (does not touch the device).
+int validate(const pk_problem* p, Algo algo, bool need_workspace);
+
+// Prepass launchers (prepass.cu).  All asynchronous on `stream`.
+int launch_prepass(const pk_problem& p, const Layout& L, Algo algo, cudaStream_t stream);
+
+// Fused kernels (fused_attention.cu).
+struct DebugDump {
+  void* ptr;
+  int bh, q_tile;
+};
+int launch_fused(const pk_problem& p, const Layout& L, Algo algo, cudaStream_t stream,
+                 const DebugDump* dump);
+
+template <typename T>
+inline T* at(const pk_problem& p, size_t off) {
+  return reinterpret_cast<T*>(static_cast<char*>(p.workspace) + off);
+}
+
+}  // namespace pk

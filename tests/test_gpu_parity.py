@@ -1,0 +1,199 @@
+"""GPU parity tests (B200): CUDA path through the C ABI vs reference-generated fixtures and
+the numpy oracle.  Integer codes, scales and orders must be bit-exact; outputs must satisfy
+max-abs <= 2e-3 and cosine >= 0.9999 on un-rounded FP32 outputs."""
+
+import numpy as np
+import pytest
+import torch
+
+import oracle
+from _util import cosine, golden_names, load_golden, short, widen16
+
+pytestmark = pytest.mark.gpu
+
+GRANS = ("per_warp", "per_thread")
+MAX_ABS = 2e-3
+MIN_COS = 0.9999
+
+
+def _inputs(g):
+    from _gpu import to_device
+    return (to_device(g["q"], g["dtype"]), to_device(g["k"], g["dtype"]), to_device(g["v"], g["dtype"]))
+
+
+def _flat(a):
+    return a.reshape(a.shape[0] * a.shape[1], *a.shape[2:])
+
+
+def _check_prepared(call, g, gran, algo):
+    from _gpu import f32
+    b, h, sq, d = g["qf"].shape
+    sk = g["kf"].shape[2]
+    bh = b * h
+    v = call.views
+    qc = call.view("q_codes", torch.int8, (bh, v.sq_pad, d)).cpu().numpy()
+    kc = call.view("k_codes", torch.int8, (bh, v.sk_pad, d)).cpu().numpy()
+    vt = call.view("v_codes_t", torch.uint8, (bh, d, v.sk_pad)).cpu().numpy()
+    assert np.array_equal(qc[:, :sq], _flat(g[f"q_codes_{gran}"]))
+    assert not qc[:, sq:].any()
+    assert np.array_equal(kc[:, :sk], _flat(g[f"k_codes_{gran}"]))
+    assert not kc[:, sk:].any()
+    want_v = _flat(g["v_codes"])
+    got_v = vt.transpose(0, 2, 1)[:, :sk]
+    assert np.array_equal(got_v.view(want_v.dtype), want_v)
+    assert not vt[:, :, sk:].any()
+    qg, kg = g[f"q_scale_{gran}"], g[f"k_scale_{gran}"]
+    got_qg = call.view("q_group_scale", torch.float32, (bh, qg.shape[2])).cpu().numpy()
+    got_kg = call.view("k_group_scale", torch.float32, (bh, kg.shape[2])).cpu().numpy()
+    assert np.array_equal(got_qg, _flat(qg))
+    assert np.array_equal(got_kg, _flat(kg))
+    vs = g["v_scale"]
+    got_vs = call.view("v_scale", torch.float32, (bh, vs.shape[2])).cpu().numpy()
+    assert np.array_equal(got_vs, _flat(vs))
+    if algo == "piper" and g["sort"]:
+        order = call.view("order", torch.int32, (bh, sk)).cpu().numpy()
+        assert np.array_equal(order, _flat(g["order"]).astype(np.int32))
+
+
+@pytest.mark.parametrize("gran", GRANS)
+@pytest.mark.parametrize("name", golden_names("piper"))
+def test_piper_prepass_bit_exact_vs_reference(name, gran):
+    from _gpu import Call
+    g = load_golden(name)
+    if g["sort"] and gran == "per_thread":
+        pytest.skip("row ordering requires per-block scales")
+    q, k, v = _inputs(g)
+    call = Call("piper", q, k, v, g["scale"], g["causal"], center=g["center"], sort=g["sort"], gran=gran,
+                k_mean=_flat(g["k_mean"])[:, 0], v_mean=_flat(g["v_mean"])[:, 0]).prepare()
+    torch.cuda.synchronize()
+    _check_prepared(call, g, gran, "piper")
+
+
+@pytest.mark.parametrize("gran", GRANS)
+@pytest.mark.parametrize("name", golden_names("sage"))
+def test_sage_prepass_bit_exact_vs_reference(name, gran):
+    from _gpu import Call
+    g = load_golden(name)
+    g["sort"] = False
+    q, k, v = _inputs(g)
+    call = Call("sage2pp", q, k, v, g["scale"], g["causal"], gran=gran, k_mean=_flat(g["k_mean"])[:, 0]).prepare()
+    torch.cuda.synchronize()
+    _check_prepared(call, g, gran, "sage2pp")
+
+
+@pytest.mark.parametrize("name", ["piper_d128_s193_bf16_center", "piper_d64_s193_f16", "piper_d128_rect_f16_center"])
+def test_means_equal_oracle_means(name):
+    from _gpu import Call
+    g = load_golden(name)
+    q, k, v = _inputs(g)
+    call = Call("piper", q, k, v, g["scale"], False, center=True).prepare()
+    torch.cuda.synchronize()
+    b, h, _, d = g["kf"].shape
+    km = call.view("k_mean", torch.float32, (b * h, d)).cpu().numpy()
+    vm = call.view("v_mean", torch.float32, (b * h, d)).cpu().numpy()
+    assert np.array_equal(km, _flat(oracle.sequence_mean(g["kf"]))[:, 0])
+    assert np.array_equal(vm, _flat(oracle.sequence_mean(g["vf"]))[:, 0])
+
+
+@pytest.mark.parametrize("name", ["piper_d128_s193_bf16_center", "piper_d64_s193_f16"])
+def test_piper_first_tile_integer_products_exact(name):
+    """S = Q8 K8^T and O = P8 V8 from tensor memory are exact integers; P codes are rne(255 e)."""
+    from _gpu import Call
+    g = load_golden(name)
+    q, k, v = _inputs(g)
+    call = Call("piper", q, k, v, g["scale"], False, center=g["center"], gran="per_warp",
+                out_dtype=torch.float32).prepare()
+    s, pc, o = call.debug_tile(bh=1, q_tile=0)
+    assert call.status()[0] == 0
+    prep = oracle.piper_prepare_oracle(g["qf"], g["kf"], g["vf"], center_value=g["center"], qk_quantization="per_warp")
+    q8 = _flat(prep["q_codes"])[1].astype(np.int32)
+    k8 = _flat(prep["k_codes"])[1].astype(np.int32)
+    v8 = _flat(prep["v_codes"])[1].astype(np.int32)
+    rows = min(128, q8.shape[0])
+    want_s = q8[:rows] @ k8[:64].T
+    assert np.array_equal(s[:rows], want_s)
+    assert np.array_equal(o[:rows], pc[:rows].astype(np.int32) @ v8[:64])
+    qs = _flat(prep["q_scale"])[1][:rows, None].astype(np.float64)
+    ks = _flat(prep["k_scale"])[1][None, :64].astype(np.float64)
+    vs = _flat(prep["v_scale"])[1][None, :64].astype(np.float64)
+    t = want_s * qs * ks * g["scale"] * np.log2(np.e) + np.log2(vs)
+    e = np.exp2(t - t.max(axis=1, keepdims=True))
+    want_p = np.rint(255.0 * e)
+    diff = np.abs(pc[:rows].astype(np.float64) - want_p)
+    assert diff.max() <= 1
+    assert (diff > 0).mean() < 0.01
+
+
+def _gpu_out(algo, g, gran, out_dtype, **kw):
+    from _gpu import Call, f32
+    q, k, v = _inputs(g)
+    call = Call(algo, q, k, v, g["scale"], g["causal"], gran=gran, out_dtype=out_dtype, **kw).fwd()
+    st = call.status()
+    assert st[0] == 0, st
+    b, h = g["qf"].shape[:2]
+    vm = None
+    if algo == "piper":
+        vm = call.view("v_mean", torch.float32, (b * h, g["qf"].shape[3])).cpu().numpy()
+    return f32(call.out), vm
+
+
+@pytest.mark.parametrize("gran", GRANS)
+@pytest.mark.parametrize("name", golden_names("piper"))
+def test_piper_output_vs_oracle_and_reference(name, gran):
+    g = load_golden(name)
+    if g["sort"] and gran == "per_thread":
+        pytest.skip("row ordering requires per-block scales")
+    out, _ = _gpu_out("piper", g, gran, torch.float32, center=g["center"], sort=g["sort"])
+    want = oracle.piper_attention_oracle(g["qf"], g["kf"], g["vf"], g["scale"], g["causal"], center_value=g["center"],
+                                         qk_quantization=gran, sort_value_rows=g["sort"])
+    mag = max(1.0, float(np.abs(want).max()))
+    assert np.isfinite(out).all()
+    assert np.abs(out - want).max() <= MAX_ABS * mag
+    assert cosine(out, want) >= MIN_COS
+    ref = g[f"out32_{gran}"]  # the reference's own FP32 output (its torch means)
+    assert np.abs(out - ref).max() <= MAX_ABS * mag
+    assert cosine(out, ref) >= MIN_COS
+
+
+@pytest.mark.parametrize("gran", GRANS)
+@pytest.mark.parametrize("name", golden_names("sage"))
+def test_sage_output_vs_oracle_and_reference(name, gran):
+    g = load_golden(name)
+    out, _ = _gpu_out("sage2pp", g, gran, torch.float32)
+    want = oracle.sage_attention_2pp_oracle(g["qf"], g["kf"], g["vf"], g["scale"], g["causal"], qk_quantization=gran)
+    assert np.isfinite(out).all()
+    assert np.abs(out - want).max() <= MAX_ABS
+    assert cosine(out, want) >= MIN_COS
+    ref = g[f"out32_{gran}"]
+    assert np.abs(out - ref).max() <= MAX_ABS
+    assert cosine(out, ref) >= MIN_COS
+
+
+@pytest.mark.parametrize("name", ["piper_d128_s193_bf16_center", "piper_d64_s193_f16_causal"])
+def test_piper_16bit_output_is_rounded_fp32_output(name):
+    g = load_golden(name)
+    dt = {"float16": torch.float16, "bfloat16": torch.bfloat16}[g["dtype"]]
+    out32, _ = _gpu_out("piper", g, "per_warp", torch.float32, center=g["center"], sort=g["sort"])
+    out16, _ = _gpu_out("piper", g, "per_warp", dt, center=g["center"], sort=g["sort"])
+    assert np.array_equal(out16, oracle.round_to_dtype(out32, short(g["dtype"])))
+
+
+def test_piper_constant_value_restored_exactly():
+    g = load_golden("piper_d64_constant_v")
+    out, _ = _gpu_out("piper", g, "per_warp", torch.float16, center=True)
+    assert np.array_equal(out, g["vf"])
+
+
+def test_piper_huge_value_stays_finite():
+    g = load_golden("piper_d128_huge_v")
+    out, _ = _gpu_out("piper", g, "per_warp", torch.float32, center=False)
+    ref = g["out32_per_warp"]
+    assert np.isfinite(out).all()
+    assert np.abs(out - ref).max() <= 2.0**-9 * max(1.0, float(np.abs(ref).max()))
+
+
+def test_run_twice_is_bitwise_deterministic():
+    g = load_golden("piper_d128_s193_bf16_center")
+    a, _ = _gpu_out("piper", g, "per_warp", torch.float32, center=True)
+    b, _ = _gpu_out("piper", g, "per_warp", torch.float32, center=True)
+    assert np.array_equal(a, b)
