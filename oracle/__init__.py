@@ -26,5 +26,5 @@ from .quantizers import (  # noqa: F401
     round_to_dtype,
     sequence_mean,
 )
-from .piper import centered_value_order, piper_attention_oracle, piper_prepare_oracle  # noqa: F401
+from .piper import centered_value_order, piper_attention_oracle, piper_prepare_oracle, piper_tile_loop  # noqa: F401
 from .sage2pp import sage_attention_2pp_oracle, sage_prepare_oracle  # noqa: F401

@@ -121,47 +121,55 @@ def piper_attention_oracle(
         sort_value_rows=sort_value_rows, k_mean=k_mean, v_mean=v_mean,
     )
     b, h, sq, d = prep["q_codes"].shape
-    sk = prep["k_codes"].shape[2]
     flat = lambda a: a.reshape(b * h, *a.shape[2:])  # noqa: E731
     q8, k8, v8 = flat(prep["q_codes"]), flat(prep["k_codes"]), flat(prep["v_codes"])
     qs, ks, vs = flat(prep["q_scale"]), flat(prep["k_scale"]), flat(prep["v_scale"])
     vmean = flat(prep["v_mean"])
     sel = range(b * h)[heads] if heads is not None else range(b * h)
     out = np.empty((len(sel), sq, d), dtype=np.float32)
-    scale32 = np.float32(scale)
-    qpos = np.arange(sq)
     for oi, bh in enumerate(sel):
-        qf = q8[bh].astype(np.float32)
-        num = np.zeros((sq, d), dtype=np.float32)
-        den = np.zeros((sq,), dtype=np.float32)
-        run_max = np.full((sq,), -np.inf, dtype=np.float32)
-        for start in range(0, sk, PV_BLOCK):
-            stop = min(start + PV_BLOCK, sk)
-            kf = k8[bh, start:stop].astype(np.float32)
-            int_scores = qf @ kf.T  # exact: |sum| < 2^24
-            scores = int_scores * qs[bh][:, None] * ks[bh][None, start:stop] * scale32
-            if is_causal:
-                kpos = np.arange(start, stop)
-                scores = np.where(kpos[None, :] > qpos[:, None], np.float32(-np.inf), scores)
-            bvs = vs[bh, start:stop]
-            shifted = scores + np.log(bvs)[None, :]
-            block_max = shifted.max(axis=-1)
-            next_max = np.maximum(run_max, block_max)
-            with np.errstate(invalid="ignore", over="ignore"):
-                old_w = np.exp(run_max - next_max)
-                cur_w = np.exp(block_max - next_max)
-                p = np.exp(scores - block_max[:, None])
-            p = np.nan_to_num(p)  # piper/reference.py:135
-            num *= old_w[:, None]
-            den = den * old_w + p.sum(axis=-1, dtype=np.float32) * cur_w
-            p8 = np.clip(np.rint(p * bvs[None, :] * P_RANGE), 0.0, P_RANGE)
-            partial = p8 @ v8[bh, start:stop].astype(np.float32)  # exact integers
-            num += partial * (cur_w[:, None] / P_RANGE)
-            run_max = next_max
-        o = num / np.maximum(den, np.float32(1e-30))[:, None]
-        o = o + vmean[bh]
-        out[oi] = o
+        out[oi] = piper_tile_loop(q8[bh], qs[bh], k8[bh], ks[bh], v8[bh], vs[bh], vmean[bh], scale, is_causal)
     out = round_to_dtype(out, out_dtype)
     if heads is None:
         out = out.reshape(b, h, sq, d)
     return out
+
+
+def piper_tile_loop(q8, qs, k8, ks, v8, vs, vmean, scale, is_causal, row0: int = 0) -> np.ndarray:
+    """The 64-key online-softmax loop of one head (piper/reference.py:93-156) for the query
+    rows given (``row0`` is the position of the first one, used by the causal mask).
+    Inputs: int8 codes ``q8 [R,D]``, ``k8 [Sk,D]``, ``v8 [Sk,D]``; per-row float32 scales
+    ``qs [R]``, ``ks [Sk]``, ``vs [Sk]``; ``vmean [1,D]``.  Returns float32 ``[R,D]``."""
+    sq, d = q8.shape
+    sk = k8.shape[0]
+    scale32 = np.float32(scale)
+    qpos = np.arange(row0, row0 + sq)
+    qf = q8.astype(np.float32)
+    num = np.zeros((sq, d), dtype=np.float32)
+    den = np.zeros((sq,), dtype=np.float32)
+    run_max = np.full((sq,), -np.inf, dtype=np.float32)
+    for start in range(0, sk, PV_BLOCK):
+        stop = min(start + PV_BLOCK, sk)
+        kf = k8[start:stop].astype(np.float32)
+        int_scores = qf @ kf.T  # exact: |sum| < 2^24
+        scores = int_scores * qs[:, None] * ks[None, start:stop] * scale32
+        if is_causal:
+            kpos = np.arange(start, stop)
+            scores = np.where(kpos[None, :] > qpos[:, None], np.float32(-np.inf), scores)
+        bvs = vs[start:stop]
+        shifted = scores + np.log(bvs)[None, :]
+        block_max = shifted.max(axis=-1)
+        next_max = np.maximum(run_max, block_max)
+        with np.errstate(invalid="ignore", over="ignore"):
+            old_w = np.exp(run_max - next_max)
+            cur_w = np.exp(block_max - next_max)
+            p = np.exp(scores - block_max[:, None])
+        p = np.nan_to_num(p)  # piper/reference.py:135
+        num *= old_w[:, None]
+        den = den * old_w + p.sum(axis=-1, dtype=np.float32) * cur_w
+        p8 = np.clip(np.rint(p * bvs[None, :] * P_RANGE), 0.0, P_RANGE)
+        partial = p8 @ v8[start:stop].astype(np.float32)  # exact integers
+        num += partial * (cur_w[:, None] / P_RANGE)
+        run_max = next_max
+    o = num / np.maximum(den, np.float32(1e-30))[:, None]
+    return o + vmean
