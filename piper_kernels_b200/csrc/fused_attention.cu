@@ -11,7 +11,7 @@
 //
 // One CTA owns a 128-row query tile of one (batch, head).  Warp roles:
 //   softmax warpgroup(s)  thread = query row = tensor-memory lane; reads the INT32 score tile,
-//                         writes the 8-bit probability tile back into tensor memory
+//                         writes the 8-bit probability tile into tensor memory
 //   dequant warpgroup     thread = query row; holds the FP32 numerator row, folds every 64-key
 //                         PV partial into it, owns the running max / denominator, writes out
 //   producer warp         TMA loads of the Q tile, K tiles, V^T tiles and per-key vectors
@@ -20,14 +20,20 @@
 // Piper's probability codes depend only on the tile's own maximum, so two softmax warpgroups
 // process alternate key tiles in parallel; Sage's depend on the running maximum, so it uses one.
 //
-// Tensor memory (512 columns): four score buffers of 64 columns (the probability tile
-// overwrites the first 16 columns of its score buffer), two PV-partial buffers of head_dim
-// columns.  No cluster launch, no multicast; every wait is time-limited.
+// INT32 accumulators are read as FP32 without an integer instruction: every INT32 buffer is
+// re-armed with the bit pattern of 1.5*2^23 by the warp that has just read it, and the next
+// product accumulates on top, so the word read back is the float 1.5*2^23 + value exactly
+// (|value| < 2^22); one packed FP32 subtract recovers the value.
+//
+// Tensor memory (512 columns): three score buffers of 64 columns, four probability buffers
+// of 16 columns, two PV-partial buffers of head_dim columns.  No cluster launch, no
+// multicast; every wait is time-limited.
 
 #include <cuda.h>
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 #include <cuda_fp8.h>
+#include <stdlib.h>
 
 #include "pk_internal.h"
 #include "pk_ptx.cuh"
@@ -39,12 +45,14 @@ constexpr int NK = 8;      // K tile ring
 constexpr int NV = 4;      // V^T tile ring
 constexpr int NVEC = 16;   // per-key vector ring (k_mul, k_add, k_inv: 3 x 64 floats)
 constexpr int NSTAT = 8;   // softmax -> dequant per-row statistics ring
-constexpr int NS = 4;      // score buffers in tensor memory
+constexpr int NS = 3;      // score buffers in tensor memory
+constexpr int NP = 4;      // probability buffers in tensor memory
 constexpr int NO = 2;      // PV partial buffers in tensor memory
 constexpr int V_LAG = 4;   // the producer issues V^T tile j together with K tile j + V_LAG
 constexpr int VEC_FLOATS = 3 * kKeyTile;
 constexpr uint32_t TMEM_COLS = 512;
-constexpr float kMagic = 12582912.f;  // 1.5 * 2^23: adding it rounds to an integer (ties to even)
+constexpr float kMagic = 12582912.f;    // 1.5 * 2^23: adding it rounds to an integer (ties to even)
+constexpr uint32_t kMagicBits = 0x4B400000u;  // bit pattern of kMagic
 
 struct FusedParams {
   const float* q_mul;   // [BH, sq_pad]
@@ -59,6 +67,7 @@ struct FusedParams {
   int32_t* status;
   void* dump;
   int dump_bh, dump_qt;
+  int ablate;  // development builds only (-DPK_TRACE): 1 skips the softmax math, 2 the dequant math
 };
 
 template <int D, int ALGO>
@@ -74,38 +83,66 @@ struct Cfg {
   static constexpr int OFF_VEC = OFF_V + NV * V_BYTES;
   static constexpr int OFF_STAT = OFF_VEC + NVEC * VEC_FLOATS * 4;
   static constexpr int OFF_BAR = OFF_STAT + NSTAT * kQTile * 8;
-  static constexpr int NUM_BARS = 1 + 2 * NK + 2 * NV + NVEC + 2 * NS + 2 * NO + NSTAT;
+  static constexpr int NUM_BARS = 1 + 2 * NK + NV + NVEC + NS + 2 * NP + NO + NSTAT;
   static constexpr int OFF_MISC = OFF_BAR + NUM_BARS * 8;
   static constexpr int SMEM_BYTES = OFF_MISC + 16 + 1024;  // + slack for 1024-byte alignment
   static constexpr uint32_t COL_S = 0;
-  static constexpr uint32_t COL_O = NS * kKeyTile;
+  static constexpr uint32_t COL_P = NS * kKeyTile;
+  static constexpr uint32_t COL_O = COL_P + NP * (kKeyTile / 4);
+  static_assert(COL_O + NO * D <= TMEM_COLS, "tensor memory budget");
 };
 
-// barrier indices
+// shared-memory addresses of the mbarriers.  One commit per product: qk_done[j % NK] is
+// observed by the softmax warpgroup (scores ready) and by the producer (K stage free);
+// pv_done[j % NP] by the dequant warpgroup (partial ready), the producer (V stage free) and
+// the softmax warpgroup (probability buffer free).
 struct Bars {
   uint32_t base;
-  __device__ uint32_t q_full() const { return base; }
-  __device__ uint32_t k_full(int i) const { return base + 8 * (1 + i); }
-  __device__ uint32_t k_empty(int i) const { return base + 8 * (1 + NK + i); }
-  __device__ uint32_t v_full(int i) const { return base + 8 * (1 + 2 * NK + i); }
-  __device__ uint32_t v_empty(int i) const { return base + 8 * (1 + 2 * NK + NV + i); }
-  __device__ uint32_t vec_full(int i) const { return base + 8 * (1 + 2 * NK + 2 * NV + i); }
-  __device__ uint32_t s_full(int i) const { return base + 8 * (1 + 2 * NK + 2 * NV + NVEC + i); }
-  __device__ uint32_t p_ready(int i) const { return base + 8 * (1 + 2 * NK + 2 * NV + NVEC + NS + i); }
-  __device__ uint32_t o_full(int i) const { return base + 8 * (1 + 2 * NK + 2 * NV + NVEC + 2 * NS + i); }
-  __device__ uint32_t o_empty(int i) const { return base + 8 * (1 + 2 * NK + 2 * NV + NVEC + 2 * NS + NO + i); }
-  __device__ uint32_t stat_full(int i) const {
-    return base + 8 * (1 + 2 * NK + 2 * NV + NVEC + 2 * NS + 2 * NO + i);
-  }
+  __device__ uint32_t at(int i) const { return base + 8 * i; }
+  __device__ uint32_t q_full() const { return at(0); }
+  __device__ uint32_t k_full(int i) const { return at(1 + i); }
+  __device__ uint32_t qk_done(int i) const { return at(1 + NK + i); }
+  __device__ uint32_t v_full(int i) const { return at(1 + 2 * NK + i); }
+  __device__ uint32_t vec_full(int i) const { return at(1 + 2 * NK + NV + i); }
+  __device__ uint32_t s_free(int i) const { return at(1 + 2 * NK + NV + NVEC + i); }
+  __device__ uint32_t p_ready(int i) const { return at(1 + 2 * NK + NV + NVEC + NS + i); }
+  __device__ uint32_t pv_done(int i) const { return at(1 + 2 * NK + NV + NVEC + NS + NP + i); }
+  __device__ uint32_t o_empty(int i) const { return at(1 + 2 * NK + NV + NVEC + NS + 2 * NP + i); }
+  __device__ uint32_t stat_full(int i) const { return at(1 + 2 * NK + NV + NVEC + NS + 2 * NP + NO + i); }
 };
+static_assert(NV == NP, "pv_done serves the V ring and the probability ring with one index");
 
 // wait-site codes reported in status[0] when a wait is abandoned
 enum : int {
-  W_PROD_K = 11, W_PROD_V = 12, W_MMA_Q = 21, W_MMA_K = 22, W_MMA_P = 23, W_MMA_O = 24, W_MMA_V = 25,
-  W_SM_VEC = 31, W_SM_S = 32, W_DQ_STAT = 41, W_DQ_O = 42
+  W_PROD_K = 11, W_PROD_V = 12, W_QK_Q = 21, W_QK_K = 22, W_QK_S = 23, W_PV_P = 26, W_PV_O = 27, W_PV_V = 28,
+  W_SM_VEC = 31, W_SM_S = 32, W_SM_PV = 33, W_DQ_STAT = 41, W_DQ_O = 42
 };
 
-__device__ __forceinline__ float round_through_f16(float x) { return __half2float(__float2half_rn(x)); }
+// Optional per-role timestamps of one CTA (development builds only: -DPK_TRACE).  Written to
+// the debug dump buffer at byte offset 256 KiB as int64 [role][tile][4], six roles.
+#ifdef PK_TRACE
+#define PK_TRACE_AT(role, tile, k)                                                                   \
+  do {                                                                                               \
+    if (dumping && (tile) < 1024 && (threadIdx.x & 31) == 0)                                          \
+      reinterpret_cast<long long*>(static_cast<char*>(prm.dump) + (256 << 10))[((role) * 1024 + (tile)) * 4 + (k)] = clock64(); \
+  } while (0)
+#else
+#define PK_TRACE_AT(role, tile, k) do { } while (0)
+#endif
+
+__device__ __forceinline__ float max3(float a, float b, float c) {
+  float r;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(r) : "f"(a), "f"(b), "f"(c));
+  return r;
+}
+
+// Stores the magic bit pattern into `ncols` (multiple of 16) columns of this thread's lane.
+__device__ __forceinline__ void tmem_arm(uint32_t addr, int ncols) {
+  uint32_t m[16];
+#pragma unroll
+  for (int i = 0; i < 16; ++i) m[i] = kMagicBits;
+  for (int c = 0; c < ncols; c += 16) tmem_st16(addr + c, m);
+}
 
 template <int D, int ALGO, bool K_PER_BLOCK>
 __global__ void __launch_bounds__(Cfg<D, ALGO>::THREADS, 1)
@@ -113,6 +150,11 @@ fused_attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
                        const __grid_constant__ CUtensorMap tm_v, const FusedParams prm) {
   using C = Cfg<D, ALGO>;
   constexpr int NSWG = C::NSWG;
+#ifdef PK_NO_O_MAGIC
+  constexpr bool O_MAGIC = false;
+#else
+  constexpr bool O_MAGIC = (ALGO == kPiper);  // the sage partial is FP32 and needs no conversion
+#endif
   extern __shared__ uint8_t smem_raw[];
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t* smem = smem_raw + (smem_base - smem_u32(smem_raw));
@@ -133,17 +175,19 @@ fused_attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
 
   if (tid == 0) {
     mbar_init(bars.q_full(), 1);
-    for (int i = 0; i < NK; ++i) { mbar_init(bars.k_full(i), 1); mbar_init(bars.k_empty(i), 1); }
-    for (int i = 0; i < NV; ++i) { mbar_init(bars.v_full(i), 1); mbar_init(bars.v_empty(i), 1); }
+    for (int i = 0; i < NK; ++i) { mbar_init(bars.k_full(i), 1); mbar_init(bars.qk_done(i), 1); }
+    for (int i = 0; i < NV; ++i) mbar_init(bars.v_full(i), 1);
     for (int i = 0; i < NVEC; ++i) mbar_init(bars.vec_full(i), 1);
-    for (int i = 0; i < NS; ++i) { mbar_init(bars.s_full(i), 1); mbar_init(bars.p_ready(i), 128); }
-    for (int i = 0; i < NO; ++i) { mbar_init(bars.o_full(i), 1); mbar_init(bars.o_empty(i), 128); }
+    for (int i = 0; i < NS; ++i) mbar_init(bars.s_free(i), 128);
+    for (int i = 0; i < NP; ++i) { mbar_init(bars.p_ready(i), 128); mbar_init(bars.pv_done(i), 1); }
+    for (int i = 0; i < NO; ++i) mbar_init(bars.o_empty(i), 128);
     for (int i = 0; i < NSTAT; ++i) mbar_init(bars.stat_full(i), 128);
     *abort_flag = 0;
     fence_barrier_init();
   }
   constexpr int PROD_WARP = (NSWG + 1) * 4;
-  constexpr int MMA_WARP = PROD_WARP + 1;
+  constexpr int QK_WARP = PROD_WARP + 1;
+  constexpr int PV_WARP = PROD_WARP + 2;
   if (warp == PROD_WARP) {
     tmem_alloc(smem_u32(const_cast<uint32_t*>(tmem_slot)), TMEM_COLS);
     tmem_relinquish();
@@ -156,9 +200,8 @@ fused_attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
   // The CTA starts with 128 (piper, 512 threads) or 168 (sage, 384 threads) registers per
   // thread; the dequant rows need more and the helper warpgroup far fewer, so each role
   // resizes its allocation on entry.
-  if (wg == NSWG + 1) {
-    setmaxnreg_dec<24>();
-  }
+  if (wg == NSWG + 1) setmaxnreg_dec<56>();
+
   if (warp == PROD_WARP) {
     // ------------------------------------------------------------------ producer
     if (lane == 0) {
@@ -169,12 +212,13 @@ fused_attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
       for (int i = 0; i < n_tiles + V_LAG; ++i) {
         if (i < n_tiles) {
           const int s = i % NK;
-          if (i >= NK && !mbar_wait_bounded(bars.k_empty(s), ((i / NK) - 1) & 1, abort_flag, W_PROD_K)) break;
+          if (i >= NK && !mbar_wait_bounded(bars.qk_done(s), ((i / NK) - 1) & 1, abort_flag, W_PROD_K)) break;
           mbar_expect_tx(bars.k_full(s), C::K_BYTES);
           tma_load_2d(smem_base + C::OFF_K + s * C::K_BYTES, &tm_k, bars.k_full(s), 0,
                       bh * prm.sk_pad + i * kKeyTile);
-          // The vector slot of tile i-NVEC was last read before the PV product of that tile was
-          // issued, which precedes the release of the K stage waited for above.
+          // The vector slot of tile i-NVEC was last read before the probabilities of that tile
+          // were published, which precedes the issue (and so the completion) of the K stage
+          // release waited for above (NVEC >= NK + NS + 2).
           const int vs = i % NVEC;
           const uint32_t vdst = smem_base + C::OFF_VEC + vs * VEC_FLOATS * 4;
           mbar_expect_tx(bars.vec_full(vs), VEC_FLOATS * 4);
@@ -186,145 +230,193 @@ fused_attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
         const int j = i - V_LAG;
         if (j >= 0 && j < n_tiles) {
           const int s = j % NV;
-          if (j >= NV && !mbar_wait_bounded(bars.v_empty(s), ((j / NV) - 1) & 1, abort_flag, W_PROD_V)) break;
+          if (j >= NV && !mbar_wait_bounded(bars.pv_done(s), ((j / NV) - 1) & 1, abort_flag, W_PROD_V)) break;
           mbar_expect_tx(bars.v_full(s), C::V_BYTES);
           tma_load_2d(smem_base + C::OFF_V + s * C::V_BYTES, &tm_v, bars.v_full(s), j * kKeyTile, bh * D);
         }
       }
     }
-  } else if (warp == MMA_WARP) {
-    // ------------------------------------------------------------------ mma issue
+  } else if (warp == QK_WARP) {
+    // ------------------------------------------------------------------ S = Q K^T issue
+    // tcgen05.mma issue costs tens of cycles per instruction, so the two products are issued
+    // by two different warps.  S_j is issued as soon as K tile j has landed and score buffer
+    // j % NS has been read and re-armed by the softmax warpgroup.
     if (lane == 0) {
       constexpr uint32_t idesc_qk = umma_idesc(kAccS32, kFmtS8, kFmtS8, kQTile, kKeyTile);
-      constexpr uint32_t idesc_pv = (ALGO == kPiper) ? umma_idesc(kAccS32, kFmtU8, kFmtS8, kQTile, D)
-                                                     : umma_idesc(kAccF32, kFmtE4M3, kFmtE4M3, kQTile, D);
       const uint64_t qdesc = umma_smem_desc(smem_base + C::OFF_Q, D);
-      bool ok = mbar_wait_bounded(bars.q_full(), 0, abort_flag, W_MMA_Q);
-      auto issue_qk = [&](int j) -> bool {
-        const int s = j % NK;
-        if (!mbar_wait_bounded(bars.k_full(s), (j / NK) & 1, abort_flag, W_MMA_K)) return false;
+      const uint64_t kdesc0 = umma_smem_desc(smem_base + C::OFF_K, D);
+      bool ok = mbar_wait_bounded(bars.q_full(), 0, abort_flag, W_QK_Q);
+      for (int j = 0; ok && j < n_tiles; ++j) {
+        PK_TRACE_AT(3, j, 0);
+        if (!mbar_wait_bounded(bars.k_full(j % NK), (j / NK) & 1, abort_flag, W_QK_K)) break;
+        if (!mbar_wait_bounded(bars.s_free(j % NS), (j / NS) & 1, abort_flag, W_QK_S)) break;
         tc_fence_after();
-        const uint64_t kdesc = umma_smem_desc(smem_base + C::OFF_K + s * C::K_BYTES, D);
+        PK_TRACE_AT(3, j, 1);
+        const uint64_t kdesc = kdesc0 + static_cast<uint64_t>(((j % NK) * C::K_BYTES) >> 4);
         const uint32_t d = tmem_base + C::COL_S + (j % NS) * kKeyTile;
 #pragma unroll
-        for (int kk = 0; kk < D / 32; ++kk) umma_i8_ss(d, qdesc + 2 * kk, kdesc + 2 * kk, idesc_qk, kk > 0);
-        tc_commit(bars.s_full(j % NS));
-        tc_commit(bars.k_empty(s));
-        return true;
-      };
-      for (int j = 0; ok && j < min(NS, n_tiles); ++j) ok = issue_qk(j);
-      for (int j = 0; ok && j < n_tiles; ++j) {
-        if (!mbar_wait_bounded(bars.p_ready(j % NS), (j / NS) & 1, abort_flag, W_MMA_P)) break;
-        if (j >= NO && !mbar_wait_bounded(bars.o_empty(j % NO), ((j / NO) - 1) & 1, abort_flag, W_MMA_O)) break;
-        const int s = j % NV;
-        if (!mbar_wait_bounded(bars.v_full(s), (j / NV) & 1, abort_flag, W_MMA_V)) break;
+        for (int kk = 0; kk < D / 32; ++kk) umma_i8_ss(d, qdesc + 2 * kk, kdesc + 2 * kk, idesc_qk, 1u);
+        tc_commit(bars.qk_done(j % NK));
+        PK_TRACE_AT(3, j, 2);
+      }
+    }
+  } else if (warp == PV_WARP) {
+    // ------------------------------------------------------------------ O_part = P V issue
+    if (lane == 0) {
+      constexpr uint32_t idesc_pv = (ALGO == kPiper) ? umma_idesc(kAccS32, kFmtU8, kFmtS8, kQTile, D)
+                                                     : umma_idesc(kAccF32, kFmtE4M3, kFmtE4M3, kQTile, D);
+      const uint64_t vdesc0 = umma_smem_desc(smem_base + C::OFF_V, kKeyTile);
+      for (int j = 0; j < n_tiles; ++j) {
+        PK_TRACE_AT(5, j, 0);
+        if (!mbar_wait_bounded(bars.p_ready(j % NP), (j / NP) & 1, abort_flag, W_PV_P)) break;
+        if (!mbar_wait_bounded(bars.o_empty(j % NO), (j / NO) & 1, abort_flag, W_PV_O)) break;
+        if (!mbar_wait_bounded(bars.v_full(j % NV), (j / NV) & 1, abort_flag, W_PV_V)) break;
         tc_fence_after();
-        const uint64_t vdesc = umma_smem_desc(smem_base + C::OFF_V + s * C::V_BYTES, kKeyTile);
+        PK_TRACE_AT(5, j, 1);
+        const uint64_t vdesc = vdesc0 + static_cast<uint64_t>(((j % NV) * C::V_BYTES) >> 4);
         const uint32_t d = tmem_base + C::COL_O + (j % NO) * D;
-        const uint32_t a = tmem_base + C::COL_S + (j % NS) * kKeyTile;
+        const uint32_t a = tmem_base + C::COL_P + (j % NP) * (kKeyTile / 4);
 #pragma unroll
         for (int kk = 0; kk < kKeyTile / 32; ++kk) {
-          if (ALGO == kPiper) umma_i8_ts(d, a + 8 * kk, vdesc + 2 * kk, idesc_pv, kk > 0);
+          if (ALGO == kPiper) umma_i8_ts(d, a + 8 * kk, vdesc + 2 * kk, idesc_pv, 1u);
           else umma_f8_ts(d, a + 8 * kk, vdesc + 2 * kk, idesc_pv, kk > 0);
         }
-        tc_commit(bars.o_full(j % NO));
-        tc_commit(bars.v_empty(s));
-        if (j + NS < n_tiles) ok = issue_qk(j + NS);
+        tc_commit(bars.pv_done(j % NP));
+        PK_TRACE_AT(5, j, 2);
       }
     }
   } else if (wg < NSWG) {
     // ------------------------------------------------------------------ softmax
-    if (NSWG == 2) setmaxnreg_inc<152>(); else setmaxnreg_dec<160>();
+    if (NSWG == 2) setmaxnreg_dec<120>(); else setmaxnreg_dec<160>();
     const int row = tid & 127;
     const uint32_t lane_addr = tmem_base + (static_cast<uint32_t>((warp & 3) * 32) << 16);
     const float qm = prm.q_mul[static_cast<long long>(bh) * prm.sq_pad + q0 + row];
     float m_run = -INFINITY;  // sage only
+    if (wg == 0) {  // arm every score buffer, then hand them to the mma warp
+      tmem_arm(lane_addr + C::COL_S, NS * kKeyTile);
+      tmem_wait_st();
+      tc_fence_before();
+      for (int i = 0; i < NS; ++i) mbar_arrive(bars.s_free(i));
+    }
     for (int j = wg; j < n_tiles; j += NSWG) {
+      if ((warp & 3) == 0) PK_TRACE_AT(wg, j, 0);
       // votes keep the warp converged for the .sync.aligned tensor-memory ops even when a wait is abandoned
       if (!__all_sync(0xffffffffu, mbar_wait_bounded(bars.vec_full(j % NVEC), (j / NVEC) & 1, abort_flag, W_SM_VEC))) break;
-      if (!__all_sync(0xffffffffu, mbar_wait_bounded(bars.s_full(j % NS), (j / NS) & 1, abort_flag, W_SM_S))) break;
+      if (!__all_sync(0xffffffffu, mbar_wait_bounded(bars.qk_done(j % NK), (j / NK) & 1, abort_flag, W_SM_S))) break;
       tc_fence_after();
+      if ((warp & 3) == 0) PK_TRACE_AT(wg, j, 1);
       const uint32_t s_addr = lane_addr + C::COL_S + (j % NS) * kKeyTile;
       uint32_t sraw[kKeyTile];
       tmem_ld32(s_addr, sraw);
       tmem_ld32(s_addr + 32, sraw + 32);
       tmem_wait_ld();
+      tmem_arm(s_addr, kKeyTile);  // the buffer goes back to the mma warp while this tile is processed
+      tmem_wait_st();
+      tc_fence_before();
+      mbar_arrive(bars.s_free(j % NS));
+      if ((warp & 3) == 0) PK_TRACE_AT(wg, j, 2);
       if (dumping && j == 0) {
         int32_t* ds = static_cast<int32_t*>(prm.dump);
 #pragma unroll
-        for (int c = 0; c < kKeyTile; ++c) ds[row * kKeyTile + c] = static_cast<int32_t>(sraw[c]);
+        for (int c = 0; c < kKeyTile; ++c) ds[row * kKeyTile + c] = static_cast<int32_t>(sraw[c] - kMagicBits);
       }
+      uint32_t packed[kKeyTile / 4];
+      float2 st;
+#ifdef PK_TRACE
+      if (prm.ablate & 1) {
+#pragma unroll
+        for (int c = 0; c < kKeyTile / 4; ++c) packed[c] = sraw[c] & 0x01010101u;
+        st = make_float2(0.f, 1.f);
+      } else
+#endif
+      {
+      // Per-key vectors of this tile in shared memory: [0,64) K scale, [64,128) additive term
+      // (log2 of the V row scale / 0, -inf on padding), [128,192) 1 / V row scale.
       const float4* vk = reinterpret_cast<const float4*>(vec_ring + (j % NVEC) * VEC_FLOATS);
-      float t[kKeyTile];
-      const float mt = K_PER_BLOCK ? qm * vec_ring[(j % NVEC) * VEC_FLOATS] : 0.f;
+      // t_c = score_c * (q_mul * k_mul_c) + k_add_c, two columns per packed FP32 instruction;
+      // the word read from tensor memory is the float 1.5*2^23 + score.
+      float2 t2[kKeyTile / 2];
+      const float mt = K_PER_BLOCK ? qm * vec_ring[(j % NVEC) * VEC_FLOATS] : qm;
+      const float2 mt2 = make_float2(mt, mt);
+      const float2 neg_magic2 = make_float2(-kMagic, -kMagic);
 #pragma unroll
       for (int c4 = 0; c4 < kKeyTile / 4; ++c4) {
         const float4 add = vk[kKeyTile / 4 + c4];
-        const float a4[4] = {add.x, add.y, add.z, add.w};
-        float m4[4] = {mt, mt, mt, mt};
-        if (!K_PER_BLOCK) {
+        const float2 f0 = __fadd2_rn(make_float2(__uint_as_float(sraw[c4 * 4 + 0]), __uint_as_float(sraw[c4 * 4 + 1])), neg_magic2);
+        const float2 f1 = __fadd2_rn(make_float2(__uint_as_float(sraw[c4 * 4 + 2]), __uint_as_float(sraw[c4 * 4 + 3])), neg_magic2);
+        if (K_PER_BLOCK) {
+          t2[c4 * 2 + 0] = __ffma2_rn(f0, mt2, make_float2(add.x, add.y));
+          t2[c4 * 2 + 1] = __ffma2_rn(f1, mt2, make_float2(add.z, add.w));
+        } else {
           const float4 mul = vk[c4];
-          m4[0] = mul.x; m4[1] = mul.y; m4[2] = mul.z; m4[3] = mul.w;
-        }
-#pragma unroll
-        for (int i = 0; i < 4; ++i) {
-          const float sf = static_cast<float>(static_cast<int32_t>(sraw[c4 * 4 + i]));
-          t[c4 * 4 + i] = K_PER_BLOCK ? fmaf(sf, m4[i], a4[i]) : fmaf(sf * qm, m4[i], a4[i]);
+          t2[c4 * 2 + 0] = __ffma2_rn(__fmul2_rn(f0, mt2), make_float2(mul.x, mul.y), make_float2(add.x, add.y));
+          t2[c4 * 2 + 1] = __ffma2_rn(__fmul2_rn(f1, mt2), make_float2(mul.z, mul.w), make_float2(add.z, add.w));
         }
       }
       if (prm.causal && j * kKeyTile + kKeyTile - 1 > q0) {
         const int lim = q0 + row - j * kKeyTile;  // columns above this index are masked
 #pragma unroll
-        for (int c = 0; c < kKeyTile; ++c)
-          if (c > lim) t[c] = -INFINITY;
+        for (int c2 = 0; c2 < kKeyTile / 2; ++c2) {
+          if (2 * c2 > lim) t2[c2].x = -INFINITY;
+          if (2 * c2 + 1 > lim) t2[c2].y = -INFINITY;
+        }
       }
-      float bm = t[0];
+      // four independent max chains
+      float bm0 = fmaxf(t2[0].x, t2[0].y), bm1 = fmaxf(t2[1].x, t2[1].y);
+      float bm2 = fmaxf(t2[2].x, t2[2].y), bm3 = fmaxf(t2[3].x, t2[3].y);
 #pragma unroll
-      for (int c = 1; c < kKeyTile; ++c) bm = fmaxf(bm, t[c]);
+      for (int c2 = 4; c2 < kKeyTile / 2; c2 += 4) {
+        bm0 = max3(bm0, t2[c2].x, t2[c2].y);
+        bm1 = max3(bm1, t2[c2 + 1].x, t2[c2 + 1].y);
+        bm2 = max3(bm2, t2[c2 + 2].x, t2[c2 + 2].y);
+        bm3 = max3(bm3, t2[c2 + 3].x, t2[c2 + 3].y);
+      }
+      const float bm = fmaxf(fmaxf(bm0, bm1), fmaxf(bm2, bm3));
 
-      uint32_t packed[kKeyTile / 4];
-      float2 st;
       if (ALGO == kPiper) {
         const float bs = (bm == -INFINITY) ? 0.f : bm;
-        float psum = 0.f;
+        const float2 nbs2 = make_float2(-bs, -bs);
+        const float2 c255 = make_float2(255.f, 255.f), magic2 = make_float2(kMagic, kMagic);
+        float2 psum_a = make_float2(0.f, 0.f), psum_b = make_float2(0.f, 0.f);
 #pragma unroll
         for (int c4 = 0; c4 < kKeyTile / 4; ++c4) {
           const float4 inv = vk[2 * (kKeyTile / 4) + c4];
-          const float i4[4] = {inv.x, inv.y, inv.z, inv.w};
-          uint32_t b[4];
-#pragma unroll
-          for (int i = 0; i < 4; ++i) {
-            const float e = ex2_approx(t[c4 * 4 + i] - bs);
-            psum = fmaf(e, i4[i], psum);
-            b[i] = __float_as_uint(fmaf(e, 255.f, kMagic));  // low byte = rne(255 e)
-          }
-          const uint32_t lo = __byte_perm(b[0], b[1], 0x0040);
-          const uint32_t hi = __byte_perm(b[2], b[3], 0x0040);
+          const float2 d0 = __fadd2_rn(t2[c4 * 2 + 0], nbs2), d1 = __fadd2_rn(t2[c4 * 2 + 1], nbs2);
+          const float2 e0 = make_float2(ex2_approx(d0.x), ex2_approx(d0.y));
+          const float2 e1 = make_float2(ex2_approx(d1.x), ex2_approx(d1.y));
+          psum_a = __ffma2_rn(e0, make_float2(inv.x, inv.y), psum_a);
+          psum_b = __ffma2_rn(e1, make_float2(inv.z, inv.w), psum_b);
+          const float2 b0 = __ffma2_rn(e0, c255, magic2), b1 = __ffma2_rn(e1, c255, magic2);  // low byte = rne(255 e)
+          const uint32_t lo = __byte_perm(__float_as_uint(b0.x), __float_as_uint(b0.y), 0x0040);
+          const uint32_t hi = __byte_perm(__float_as_uint(b1.x), __float_as_uint(b1.y), 0x0040);
           packed[c4] = __byte_perm(lo, hi, 0x5410);
         }
-        st = make_float2(bm, psum);
+        st = make_float2(bm, (psum_a.x + psum_a.y) + (psum_b.x + psum_b.y));
       } else {
         const float nm = fmaxf(m_run, bm);
         const float ns = (nm == -INFINITY) ? 0.f : nm;
         const float ow = (m_run == nm) ? 1.f : ex2_approx(m_run - ns);
-        const float off = ns - 8.807354922057604f;  // log2(448): P = e4m3(448 * 2^(t - max))
-        float psum = 0.f;
+        const float off = 8.807354922057604f - ns;  // log2(448): P = e4m3(448 * 2^(t - max))
+        const float2 off2 = make_float2(off, off);
+        float2 psum2 = make_float2(0.f, 0.f);
 #pragma unroll
         for (int c4 = 0; c4 < kKeyTile / 4; ++c4) {
-          float e[4];
-#pragma unroll
-          for (int i = 0; i < 4; ++i) {
-            e[i] = ex2_approx(t[c4 * 4 + i] - off);
-            psum += e[i];
-          }
-          const uint32_t lo = __nv_cvt_float2_to_fp8x2(make_float2(e[0], e[1]), __NV_SATFINITE, __NV_E4M3);
-          const uint32_t hi = __nv_cvt_float2_to_fp8x2(make_float2(e[2], e[3]), __NV_SATFINITE, __NV_E4M3);
-          packed[c4] = lo | (hi << 16);
+          const float2 d0 = __fadd2_rn(t2[c4 * 2 + 0], off2), d1 = __fadd2_rn(t2[c4 * 2 + 1], off2);
+          const float2 e0 = make_float2(ex2_approx(d0.x), ex2_approx(d0.y));
+          const float2 e1 = make_float2(ex2_approx(d1.x), ex2_approx(d1.y));
+          psum2 = __fadd2_rn(psum2, __fadd2_rn(e0, e1));
+          const uint32_t lo = __nv_cvt_float2_to_fp8x2(e0, __NV_SATFINITE, __NV_E4M3);
+          const uint32_t hi = __nv_cvt_float2_to_fp8x2(e1, __NV_SATFINITE, __NV_E4M3);
+          packed[c4] = __byte_perm(lo, hi, 0x5410);
         }
-        st = make_float2(ow, psum * (1.f / 448.f));
+        st = make_float2(ow, (psum2.x + psum2.y) * (1.f / 448.f));
         m_run = nm;
       }
-      tmem_st16(s_addr, packed);
+      }
+      // probability buffer j%NP was last read by the PV product of tile j-NP
+      if (j >= NP && !__all_sync(0xffffffffu, mbar_wait_bounded(bars.pv_done(j % NP), ((j / NP) - 1) & 1, abort_flag, W_SM_PV))) break;
+      tc_fence_after();
+      tmem_st16(lane_addr + C::COL_P + (j % NP) * (kKeyTile / 4), packed);
       tmem_wait_st();
       stat_ring[(j % NSTAT) * kQTile + row] = st;
       if (dumping && j == 0) {
@@ -333,22 +425,32 @@ fused_attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
         for (int c = 0; c < kKeyTile / 4; ++c) dp[row * (kKeyTile / 4) + c] = packed[c];
       }
       tc_fence_before();
-      mbar_arrive(bars.p_ready(j % NS));
+      mbar_arrive(bars.p_ready(j % NP));
       mbar_arrive(bars.stat_full(j % NSTAT));
+      if ((warp & 3) == 0) PK_TRACE_AT(wg, j, 3);
     }
   } else if (wg == NSWG) {
     // ------------------------------------------------------------------ dequant + epilogue
-    if (NSWG == 2) setmaxnreg_inc<184>(); else setmaxnreg_inc<216>();
+    if (NSWG == 2) setmaxnreg_inc<216>(); else setmaxnreg_inc<216>();
     const int row = tid & 127;
     const uint32_t lane_addr = tmem_base + (static_cast<uint32_t>((warp & 3) * 32) << 16);
-    float num[D];
+    if (O_MAGIC) {
+      tmem_arm(lane_addr + C::COL_O, NO * D);
+      tmem_wait_st();
+    }
+    tc_fence_before();
+    for (int i = 0; i < NO; ++i) mbar_arrive(bars.o_empty(i));
+
+    float2 num2[D / 2];
 #pragma unroll
-    for (int d = 0; d < D; ++d) num[d] = 0.f;
+    for (int d = 0; d < D / 2; ++d) num2[d] = make_float2(0.f, 0.f);
     float den = 0.f, m = -INFINITY;
     bool ok = true;
     for (int j = 0; j < n_tiles; ++j) {
+      if ((warp & 3) == 0) PK_TRACE_AT(2, j, 0);
       if (!__all_sync(0xffffffffu, mbar_wait_bounded(bars.stat_full(j % NSTAT), (j / NSTAT) & 1, abort_flag, W_DQ_STAT))) { ok = false; break; }
       const float2 st = stat_ring[(j % NSTAT) * kQTile + row];
+      if ((warp & 3) == 0) PK_TRACE_AT(2, j, 1);
       float ow, c;
       if (ALGO == kPiper) {
         const float bm = st.x;
@@ -367,31 +469,55 @@ fused_attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
         den = fmaf(den, ow, st.y);
         c = 1.f;
       }
-      if (!__all_sync(0xffffffffu, mbar_wait_bounded(bars.o_full(j % NO), (j / NO) & 1, abort_flag, W_DQ_O))) { ok = false; break; }
+      if (!__all_sync(0xffffffffu, mbar_wait_bounded(bars.pv_done(j % NP), (j / NP) & 1, abort_flag, W_DQ_O))) { ok = false; break; }
       tc_fence_after();
-      if (__any_sync(0xffffffffu, ow != 1.f)) {
-#pragma unroll
-        for (int d = 0; d < D; ++d) num[d] *= ow;
-      }
+      if ((warp & 3) == 0) PK_TRACE_AT(2, j, 2);
       const uint32_t o_addr = lane_addr + C::COL_O + (j % NO) * D;
+      // The partial is read 16 columns at a time; the next chunk's load is in flight while the
+      // current one is folded into the numerator, and each chunk is re-armed as soon as read.
+      uint32_t obuf[2][16];
+      tmem_ld16(o_addr, obuf[0]);
+      if (__any_sync(0xffffffffu, ow != 1.f)) {
+        const float2 ow2 = make_float2(ow, ow);
 #pragma unroll
-      for (int ch = 0; ch < D / 32; ++ch) {
-        uint32_t o[32];
-        tmem_ld32(o_addr + ch * 32, o);
+        for (int d = 0; d < D / 2; ++d) num2[d] = __fmul2_rn(num2[d], ow2);
+      }
+      const float2 c2 = make_float2(c, c);
+      const float2 neg_magic2 = make_float2(-kMagic, -kMagic);
+      if ((warp & 3) == 0) PK_TRACE_AT(4, j, 0);
+#pragma unroll
+      for (int ch = 0; ch < D / 16; ++ch) {
         tmem_wait_ld();
+        if ((warp & 3) == 0 && ch == 0) PK_TRACE_AT(4, j, 1);
+        if ((warp & 3) == 0 && ch == 1) PK_TRACE_AT(4, j, 2);
+        if (ch + 1 < D / 16) tmem_ld16(o_addr + (ch + 1) * 16, obuf[(ch + 1) & 1]);
+        if (O_MAGIC) tmem_arm(o_addr + ch * 16, 16);
+        const uint32_t* o = obuf[ch & 1];
         if (dumping && j == 0) {
           uint32_t* dp = reinterpret_cast<uint32_t*>(static_cast<char*>(prm.dump) + kQTile * kKeyTile * 5);
 #pragma unroll
-          for (int i = 0; i < 32; ++i) dp[row * D + ch * 32 + i] = o[i];
+          for (int i = 0; i < 16; ++i) dp[row * D + ch * 16 + i] = O_MAGIC ? o[i] - kMagicBits : o[i];
         }
+#ifdef PK_TRACE
+        if (prm.ablate & 2) { num2[ch].x += __uint_as_float(o[0] ^ o[15]); continue; }
+#endif
 #pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          if (ALGO == kPiper) num[ch * 32 + i] = fmaf(static_cast<float>(static_cast<int32_t>(o[i])), c, num[ch * 32 + i]);
-          else num[ch * 32 + i] += round_through_f16(__uint_as_float(o[i]));
+        for (int i = 0; i < 8; ++i) {
+          float2 y = make_float2(__uint_as_float(o[2 * i]), __uint_as_float(o[2 * i + 1]));
+          if (ALGO == kPiper && !O_MAGIC) y = make_float2(__uint_as_float(o[2 * i] + kMagicBits), __uint_as_float(o[2 * i + 1] + kMagicBits));
+          if (ALGO == kPiper) {
+            // the word is the float 1.5*2^23 + partial; num += partial * c
+            num2[ch * 8 + i] = __ffma2_rn(__fadd2_rn(y, neg_magic2), c2, num2[ch * 8 + i]);
+          } else {
+            num2[ch * 8 + i] = __fadd2_rn(num2[ch * 8 + i], __half22float2(__floats2half2_rn(y.x, y.y)));
+          }
         }
       }
+      if ((warp & 3) == 0) PK_TRACE_AT(4, j, 3);
+      if (O_MAGIC) tmem_wait_st();
       tc_fence_before();
       mbar_arrive(bars.o_empty(j % NO));
+      if ((warp & 3) == 0) PK_TRACE_AT(2, j, 3);
     }
     // epilogue: normalise, restore the V mean (piper) / apply the channel scale (sage), cast
     const int grow = q0 + row;
@@ -404,8 +530,9 @@ fused_attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
         float r[8];
 #pragma unroll
         for (int i = 0; i < 8; ++i) {
-          if (ALGO == kPiper) r[i] = __fdiv_rn(num[d0 + i], dmax) + aux[d0 + i];
-          else r[i] = __fdiv_rn(num[d0 + i] * __fdiv_rn(aux[d0 + i], 448.f), dmax);
+          const float nv = (i & 1) ? num2[(d0 + i) / 2].y : num2[(d0 + i) / 2].x;
+          if (ALGO == kPiper) r[i] = __fdiv_rn(nv, dmax) + aux[d0 + i];
+          else r[i] = __fdiv_rn(nv * __fdiv_rn(aux[d0 + i], 448.f), dmax);
         }
         if (prm.out_dtype == PK_F32) {
           float4* o = reinterpret_cast<float4*>(static_cast<float*>(prm.out) + obase + d0);
@@ -495,6 +622,10 @@ int launch_one(const pk_problem& p, const Layout& L, cudaStream_t st, const Debu
   prm.dump = dump ? dump->ptr : nullptr;
   prm.dump_bh = dump ? dump->bh : -1;
   prm.dump_qt = dump ? dump->q_tile : -1;
+  prm.ablate = 0;
+#ifdef PK_TRACE
+  if (const char* a = getenv("PK_ABLATE")) prm.ablate = atoi(a);
+#endif
   auto kern = fused_attention_kernel<D, ALGO, KPB>;
   {
     const cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES);

@@ -41,6 +41,19 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
   return ok != 0;
 }
 
+// Non-blocking probe of a phase (used where one thread polls several barriers).
+__device__ __forceinline__ bool mbar_test_wait(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+
 // Wait limit: ~1.5e9 SM cycles (well under a second at any clock this part runs at).
 constexpr long long kWaitCycleLimit = 1500000000LL;
 
@@ -53,6 +66,9 @@ __device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity,
   uint32_t polls = 0;
   while (true) {
     if (mbar_try_wait(bar, parity)) return true;
+#ifdef PK_WAIT_SLEEP
+    __nanosleep(PK_WAIT_SLEEP);
+#endif
     if ((++polls & 0x3FF) == 0) {
       if (*abort_flag != 0) return false;
       if (clock64() - t0 > kWaitCycleLimit) {

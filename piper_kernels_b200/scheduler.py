@@ -1,0 +1,51 @@
+"""Host scheduler: shard the flattened (batch x heads) axis across the GPUs of one box.
+
+Every (batch, head) of an attention call is independent (its softmax, K mean, V mean / scale
+and key order are all per head), so the path needs no collective: each rank runs the prepass
+and the fused kernel on a contiguous chunk of flat heads and keeps its slice of the output.
+Outputs are gathered only when a caller asks for the whole tensor (for reporting).
+"""
+
+from __future__ import annotations
+
+import torch
+
+
+def shard_heads(flat_heads: int, world: int, rank: int) -> range:
+    """Contiguous, balanced chunk of ``range(flat_heads)`` owned by ``rank``."""
+    if world <= 0 or not 0 <= rank < world:
+        raise ValueError(f"bad rank {rank} of {world}")
+    base, extra = divmod(flat_heads, world)
+    start = rank * base + min(rank, extra)
+    return range(start, start + base + (1 if rank < extra else 0))
+
+
+def sharded_attention(op, query, key, value, *, world: int, rank: int, **kwargs) -> tuple[torch.Tensor, range]:
+    """Run ``op`` (``piper_attention`` / ``sage_attention_2pp`` or any function with their
+    signature) on this rank's heads.  Inputs are full ``[B,H,S,D]`` tensors (or views of
+    them); returns the output slice ``[1, n_local, Sq, D]`` and the flat-head range."""
+    b, h = query.shape[:2]
+    mine = shard_heads(b * h, world, rank)
+    flat = lambda t: t.reshape(b * h, *t.shape[2:]) if t.is_contiguous() else t.flatten(0, 1)  # noqa: E731
+    if len(mine) == 0:
+        return query.new_empty((1, 0, query.shape[2], query.shape[3])), mine
+    sl = slice(mine.start, mine.stop)
+    out = op(flat(query)[sl].unsqueeze(0), flat(key)[sl].unsqueeze(0), flat(value)[sl].unsqueeze(0), **kwargs)
+    return out, mine
+
+
+def gather_outputs(local: torch.Tensor, mine: range, flat_heads: int, shape, group=None) -> torch.Tensor | None:
+    """Collect every rank's slice on rank 0 (reporting only; not part of the timed path)."""
+    import torch.distributed as dist
+
+    world = dist.get_world_size(group)
+    rank = dist.get_rank(group)
+    pieces = [None] * world
+    dist.gather_object((mine.start, mine.stop, local.cpu()), pieces if rank == 0 else None, dst=0, group=group)
+    if rank != 0:
+        return None
+    full = torch.empty((flat_heads, *shape[2:]), dtype=local.dtype)
+    for start, stop, piece in pieces:
+        if stop > start:
+            full[start:stop] = piece[0]
+    return full.reshape(shape)

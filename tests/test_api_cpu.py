@@ -1,0 +1,145 @@
+"""CPU tests of the host side: validation messages mirror the reference's, the C ABI library
+loads and exports every declared symbol, and argument errors come back as codes (no GPU)."""
+
+import ctypes as C
+import re
+from pathlib import Path
+
+import pytest
+import torch
+
+import piper_kernels_b200 as pk
+from piper_kernels_b200 import _cabi, _ops
+from piper_kernels_b200.attention.piper import default_center_value, should_sort_value_rows
+
+ROOT = Path(__file__).resolve().parents[1]
+
+
+def _qkv(dtype=torch.float16, sq=8, sk=8, d=64, b=1, h=2):
+    return (torch.randn(b, h, sq, d).to(dtype), torch.randn(b, h, sk, d).to(dtype), torch.randn(b, h, sk, d).to(dtype))
+
+
+@pytest.mark.parametrize("fn,name", [(pk.piper_attention, "Piper Attention"), (pk.sage_attention_2pp, "SageAttention2++")])
+def test_validation_messages(fn, name):
+    q, k, v = _qkv()
+    with pytest.raises(ValueError, match="float16 or bfloat16"):
+        fn(q.float(), k.float(), v.float())
+    with pytest.raises(ValueError, match="share a dtype"):
+        fn(q, k.to(torch.bfloat16), v)
+    with pytest.raises(ValueError, match="head dimensions 64 and 128"):
+        fn(*_qkv(d=32))
+    with pytest.raises(ValueError, match="key/value lengths"):
+        fn(q, k, v[:, :, :4])
+    with pytest.raises(ValueError, match="equal batch and head dimensions"):
+        fn(q, k[:, :1], v[:, :1])
+    with pytest.raises(ValueError, match="equal query and key lengths"):
+        fn(*_qkv(sq=4, sk=8), is_causal=True)
+    with pytest.raises(ValueError, match="does not accept empty"):
+        fn(q[:, :, :0], k, v)
+    with pytest.raises(ValueError, match="head dimension must be contiguous"):
+        fn(q.transpose(2, 3).contiguous().transpose(2, 3), k, v)
+    with pytest.raises(ValueError, match="finite and positive"):
+        fn(q, k, v, scale=0.0)
+    with pytest.raises(ValueError, match="shape"):
+        fn(q[0], k[0], v[0])
+    with pytest.raises(RuntimeError, match="inference-only"):
+        fn(q.requires_grad_(), k, v)
+    assert name in str(pytest.raises(ValueError, fn, q.detach().float(), k.float(), v.float()).value)
+
+
+def test_no_cpu_fallback():
+    q, k, v = _qkv()
+    with pytest.raises(RuntimeError, match="no CPU path"):
+        pk.piper_attention(q, k, v)
+    with pytest.raises(RuntimeError, match="no CPU path"):
+        pk.sage_attention_2pp(q, k, v)
+
+
+def test_default_policies():
+    q = torch.empty(1, 1, 1024, 128, device="meta")
+    assert not default_center_value(torch.empty(1, 1, 1024, 128), torch.empty(1, 1, 1024, 128), False)  # CPU tensor
+    assert should_sort_value_rows(center_value=True, is_causal=False, head_dim=128, key_length=16384)
+    assert not should_sort_value_rows(center_value=True, is_causal=False, head_dim=128, key_length=16383)
+    assert not should_sort_value_rows(center_value=False, is_causal=False, head_dim=128, key_length=32768)
+    assert not should_sort_value_rows(center_value=True, is_causal=True, head_dim=128, key_length=32768)
+    assert not should_sort_value_rows(center_value=True, is_causal=False, head_dim=64, key_length=32768)
+    del q
+
+
+def test_library_exports_every_declared_symbol():
+    header = (ROOT / "include" / "piper_b200.h").read_text()
+    declared = set(re.findall(r"PK_API\s+(?:const\s+char\*|int)\s+(pk_\w+)\(", header))
+    assert declared == set(_cabi.EXPORTS)
+    lib = _cabi.lib()
+    for name in declared:
+        assert hasattr(lib, name), name
+    assert lib.pk_version() == 1
+
+
+def test_struct_layout_matches_header(tmp_path):
+    """The ctypes mirror must agree with what a C compiler makes of include/piper_b200.h."""
+    import shutil
+    import subprocess
+
+    if shutil.which("gcc") is None:
+        pytest.skip("gcc not available")
+    fields_p = [f[0] for f in _cabi.PkProblem._fields_]
+    fields_v = [f[0] for f in _cabi.PkViews._fields_]
+    src = ['#include <stdio.h>', '#include <stddef.h>', f'#include "{ROOT}/include/piper_b200.h"', "int main(void){",
+           'printf("%zu %zu\\n", sizeof(pk_problem), sizeof(pk_views));']
+    src += [f'printf("%zu\\n", offsetof(pk_problem, {f}));' for f in fields_p]
+    src += [f'printf("%zu\\n", offsetof(pk_views, {f}));' for f in fields_v]
+    src += ["return 0;}"]
+    (tmp_path / "layout.c").write_text("\n".join(src))
+    subprocess.run(["gcc", "-o", str(tmp_path / "layout"), str(tmp_path / "layout.c")], check=True)
+    out = subprocess.run([str(tmp_path / "layout")], check=True, capture_output=True, text=True).stdout.split()
+    nums = [int(x) for x in out]
+    assert nums[0] == C.sizeof(_cabi.PkProblem) and nums[1] == C.sizeof(_cabi.PkViews)
+    want = [getattr(_cabi.PkProblem, f).offset for f in fields_p] + [getattr(_cabi.PkViews, f).offset for f in fields_v]
+    assert nums[2:] == want
+
+
+def _problem(**over):
+    p = _cabi.PkProblem()
+    p.batch, p.heads, p.q_len, p.kv_len, p.head_dim = 1, 2, 100, 200, 128
+    p.in_dtype = p.out_dtype = _cabi.PK_BF16
+    p.scale = 0.1
+    p.q = p.k = p.v = 256
+    for k_, v_ in over.items():
+        setattr(p, k_, v_)
+    return p
+
+
+def test_abi_argument_errors_without_gpu():
+    lib = _cabi.lib()
+    n = C.c_uint64()
+    assert lib.pk_piper_workspace_bytes(C.byref(_problem()), C.byref(n)) == _cabi.PK_OK
+    assert n.value > 2 * (128 * 128 + 256 * 128 * 2)
+    bad = [dict(head_dim=96), dict(q_len=0), dict(in_dtype=_cabi.PK_F32), dict(scale=float("nan")),
+           dict(is_causal=1), dict(qk_granularity=7), dict(sort_value_rows=1), dict(q=None)]
+    for over in bad:
+        assert lib.pk_piper_workspace_bytes(C.byref(_problem(**over)), C.byref(n)) == _cabi.PK_ERR_BAD_ARG, over
+        assert lib.pk_last_error()
+    assert lib.pk_sage2pp_workspace_bytes(C.byref(_problem(head_dim=64)), C.byref(n)) == _cabi.PK_OK
+    # run without a workspace is refused before anything touches a device
+    p = _problem(out=256)
+    assert lib.pk_piper_attention_fwd(C.byref(p)) == _cabi.PK_ERR_WORKSPACE
+    p.workspace, p.workspace_bytes = 4096, 16
+    assert lib.pk_piper_attention_fwd(C.byref(p)) == _cabi.PK_ERR_WORKSPACE
+    assert b"too small" in lib.pk_last_error()
+
+
+def test_workspace_grows_with_sorting_and_granularity():
+    lib = _cabi.lib()
+    a, b = C.c_uint64(), C.c_uint64()
+    lib.pk_piper_workspace_bytes(C.byref(_problem(center_value=1)), C.byref(a))
+    lib.pk_piper_workspace_bytes(C.byref(_problem(center_value=1, sort_value_rows=1)), C.byref(b))
+    assert b.value > a.value
+
+
+def test_fake_kernel_shapes():
+    q = torch.empty(2, 3, 5, 64, dtype=torch.float16, device="meta").permute(1, 0, 2, 3)
+    out = _ops.piper_attention_op(q, q, q, 0.125, False, False)
+    assert out.shape == q.shape and out.is_contiguous() and out.dtype == q.dtype
+    out = _ops.sage_attention_2pp_op(q, q, q, 0.125, False)
+    assert out.shape == q.shape and out.is_contiguous()
