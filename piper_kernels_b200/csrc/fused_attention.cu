@@ -144,7 +144,7 @@ __device__ __forceinline__ void tmem_arm(uint32_t addr, int ncols) {
   for (int c = 0; c < ncols; c += 16) tmem_st16(addr + c, m);
 }
 
-template <int D, int ALGO, bool K_PER_BLOCK>
+template <int D, int ALGO, bool K_PER_BLOCK, bool DUMP>
 __global__ void __launch_bounds__(Cfg<D, ALGO>::THREADS, 1)
 fused_attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                        const __grid_constant__ CUtensorMap tm_v, const FusedParams prm) {
@@ -171,7 +171,8 @@ fused_attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
   const int q0 = qt * kQTile;
   const int n_all = prm.sk_pad / kKeyTile;
   const int n_tiles = prm.causal ? min(n_all, 2 * qt + 2) : n_all;
-  const bool dumping = prm.dump != nullptr && bh == prm.dump_bh && qt == prm.dump_qt;
+  // DUMP instantiations (debug entry point only) copy the first key tile's intermediates out
+  const bool dumping = DUMP && prm.dump != nullptr && bh == prm.dump_bh && qt == prm.dump_qt;
 
   if (tid == 0) {
     mbar_init(bars.q_full(), 1);
@@ -213,6 +214,13 @@ fused_attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
         if (i < n_tiles) {
           const int s = i % NK;
           if (i >= NK && !mbar_wait_bounded(bars.qk_done(s), ((i / NK) - 1) & 1, abort_flag, W_PROD_K)) break;
+#ifdef PK_TRACE
+          if ((prm.ablate & 4) && i >= NVEC) {  // development: re-use stale tiles instead of loading
+            mbar_arrive(bars.k_full(s));
+            mbar_arrive(bars.vec_full(i % NVEC));
+          } else
+#endif
+          {
           mbar_expect_tx(bars.k_full(s), C::K_BYTES);
           tma_load_2d(smem_base + C::OFF_K + s * C::K_BYTES, &tm_k, bars.k_full(s), 0,
                       bh * prm.sk_pad + i * kKeyTile);
@@ -226,13 +234,20 @@ fused_attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
           bulk_load(vdst, prm.k_mul + off, kKeyTile * 4, bars.vec_full(vs));
           bulk_load(vdst + kKeyTile * 4, prm.k_add + off, kKeyTile * 4, bars.vec_full(vs));
           bulk_load(vdst + 2 * kKeyTile * 4, prm.k_inv + off, kKeyTile * 4, bars.vec_full(vs));
+          }
         }
         const int j = i - V_LAG;
         if (j >= 0 && j < n_tiles) {
           const int s = j % NV;
           if (j >= NV && !mbar_wait_bounded(bars.pv_done(s), ((j / NV) - 1) & 1, abort_flag, W_PROD_V)) break;
-          mbar_expect_tx(bars.v_full(s), C::V_BYTES);
-          tma_load_2d(smem_base + C::OFF_V + s * C::V_BYTES, &tm_v, bars.v_full(s), j * kKeyTile, bh * D);
+#ifdef PK_TRACE
+          if ((prm.ablate & 4) && j >= NV) mbar_arrive(bars.v_full(s));
+          else
+#endif
+          {
+            mbar_expect_tx(bars.v_full(s), C::V_BYTES);
+            tma_load_2d(smem_base + C::OFF_V + s * C::V_BYTES, &tm_v, bars.v_full(s), j * kKeyTile, bh * D);
+          }
         }
       }
     }
@@ -287,7 +302,7 @@ fused_attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
     }
   } else if (wg < NSWG) {
     // ------------------------------------------------------------------ softmax
-    if (NSWG == 2) setmaxnreg_dec<120>(); else setmaxnreg_dec<160>();
+    if (NSWG == 2) setmaxnreg_dec<112>(); else setmaxnreg_dec<128>();
     const int row = tid & 127;
     const uint32_t lane_addr = tmem_base + (static_cast<uint32_t>((warp & 3) * 32) << 16);
     const float qm = prm.q_mul[static_cast<long long>(bh) * prm.sq_pad + q0 + row];
@@ -298,6 +313,10 @@ fused_attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
       tc_fence_before();
       for (int i = 0; i < NS; ++i) mbar_arrive(bars.s_free(i));
     }
+    // The tile is processed 16 columns at a time in two rolled passes over tensor memory (max,
+    // then probabilities), which keeps the loop body small enough for the instruction cache
+    // that three different roles share; the chunk after the current one is always in flight.
+    const float2 neg_magic2 = make_float2(-kMagic, -kMagic);
     for (int j = wg; j < n_tiles; j += NSWG) {
       if ((warp & 3) == 0) PK_TRACE_AT(wg, j, 0);
       // votes keep the warp converged for the .sync.aligned tensor-memory ops even when a wait is abandoned
@@ -306,132 +325,141 @@ fused_attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
       tc_fence_after();
       if ((warp & 3) == 0) PK_TRACE_AT(wg, j, 1);
       const uint32_t s_addr = lane_addr + C::COL_S + (j % NS) * kKeyTile;
-      uint32_t sraw[kKeyTile];
-      tmem_ld32(s_addr, sraw);
-      tmem_ld32(s_addr + 32, sraw + 32);
-      tmem_wait_ld();
-      tmem_arm(s_addr, kKeyTile);  // the buffer goes back to the mma warp while this tile is processed
-      tmem_wait_st();
-      tc_fence_before();
-      mbar_arrive(bars.s_free(j % NS));
-      if ((warp & 3) == 0) PK_TRACE_AT(wg, j, 2);
-      if (dumping && j == 0) {
-        int32_t* ds = static_cast<int32_t*>(prm.dump);
-#pragma unroll
-        for (int c = 0; c < kKeyTile; ++c) ds[row * kKeyTile + c] = static_cast<int32_t>(sraw[c] - kMagicBits);
-      }
-      uint32_t packed[kKeyTile / 4];
-      float2 st;
-#ifdef PK_TRACE
-      if (prm.ablate & 1) {
-#pragma unroll
-        for (int c = 0; c < kKeyTile / 4; ++c) packed[c] = sraw[c] & 0x01010101u;
-        st = make_float2(0.f, 1.f);
-      } else
-#endif
-      {
       // Per-key vectors of this tile in shared memory: [0,64) K scale, [64,128) additive term
       // (log2 of the V row scale / 0, -inf on padding), [128,192) 1 / V row scale.
       const float4* vk = reinterpret_cast<const float4*>(vec_ring + (j % NVEC) * VEC_FLOATS);
-      // t_c = score_c * (q_mul * k_mul_c) + k_add_c, two columns per packed FP32 instruction;
-      // the word read from tensor memory is the float 1.5*2^23 + score.
-      float2 t2[kKeyTile / 2];
       const float mt = K_PER_BLOCK ? qm * vec_ring[(j % NVEC) * VEC_FLOATS] : qm;
       const float2 mt2 = make_float2(mt, mt);
-      const float2 neg_magic2 = make_float2(-kMagic, -kMagic);
-#pragma unroll
-      for (int c4 = 0; c4 < kKeyTile / 4; ++c4) {
-        const float4 add = vk[kKeyTile / 4 + c4];
-        const float2 f0 = __fadd2_rn(make_float2(__uint_as_float(sraw[c4 * 4 + 0]), __uint_as_float(sraw[c4 * 4 + 1])), neg_magic2);
-        const float2 f1 = __fadd2_rn(make_float2(__uint_as_float(sraw[c4 * 4 + 2]), __uint_as_float(sraw[c4 * 4 + 3])), neg_magic2);
-        if (K_PER_BLOCK) {
-          t2[c4 * 2 + 0] = __ffma2_rn(f0, mt2, make_float2(add.x, add.y));
-          t2[c4 * 2 + 1] = __ffma2_rn(f1, mt2, make_float2(add.z, add.w));
-        } else {
-          const float4 mul = vk[c4];
-          t2[c4 * 2 + 0] = __ffma2_rn(__fmul2_rn(f0, mt2), make_float2(mul.x, mul.y), make_float2(add.x, add.y));
-          t2[c4 * 2 + 1] = __ffma2_rn(__fmul2_rn(f1, mt2), make_float2(mul.z, mul.w), make_float2(add.z, add.w));
-        }
-      }
-      if (prm.causal && j * kKeyTile + kKeyTile - 1 > q0) {
-        const int lim = q0 + row - j * kKeyTile;  // columns above this index are masked
-#pragma unroll
-        for (int c2 = 0; c2 < kKeyTile / 2; ++c2) {
-          if (2 * c2 > lim) t2[c2].x = -INFINITY;
-          if (2 * c2 + 1 > lim) t2[c2].y = -INFINITY;
-        }
-      }
-      // four independent max chains
-      float bm0 = fmaxf(t2[0].x, t2[0].y), bm1 = fmaxf(t2[1].x, t2[1].y);
-      float bm2 = fmaxf(t2[2].x, t2[2].y), bm3 = fmaxf(t2[3].x, t2[3].y);
-#pragma unroll
-      for (int c2 = 4; c2 < kKeyTile / 2; c2 += 4) {
-        bm0 = max3(bm0, t2[c2].x, t2[c2].y);
-        bm1 = max3(bm1, t2[c2 + 1].x, t2[c2 + 1].y);
-        bm2 = max3(bm2, t2[c2 + 2].x, t2[c2 + 2].y);
-        bm3 = max3(bm3, t2[c2 + 3].x, t2[c2 + 3].y);
-      }
-      const float bm = fmaxf(fmaxf(bm0, bm1), fmaxf(bm2, bm3));
+      const bool diag = prm.causal && (j * kKeyTile + kKeyTile - 1 > q0);
+      const int lim = q0 + row - j * kKeyTile;  // causal: columns above this index are masked
 
-      if (ALGO == kPiper) {
-        const float bs = (bm == -INFINITY) ? 0.f : bm;
-        const float2 nbs2 = make_float2(-bs, -bs);
-        const float2 c255 = make_float2(255.f, 255.f), magic2 = make_float2(kMagic, kMagic);
-        float2 psum_a = make_float2(0.f, 0.f), psum_b = make_float2(0.f, 0.f);
+      // t_c = score_c * (q_mul * k_mul_c) + k_add_c for the 16 columns of chunk `ch`, two columns
+      // per packed FP32 instruction; the word read from tensor memory is the float 1.5*2^23 + score.
+      auto scores16 = [&](const uint32_t* sr, int ch, float2* t2) {
 #pragma unroll
-        for (int c4 = 0; c4 < kKeyTile / 4; ++c4) {
-          const float4 inv = vk[2 * (kKeyTile / 4) + c4];
-          const float2 d0 = __fadd2_rn(t2[c4 * 2 + 0], nbs2), d1 = __fadd2_rn(t2[c4 * 2 + 1], nbs2);
-          const float2 e0 = make_float2(ex2_approx(d0.x), ex2_approx(d0.y));
-          const float2 e1 = make_float2(ex2_approx(d1.x), ex2_approx(d1.y));
-          psum_a = __ffma2_rn(e0, make_float2(inv.x, inv.y), psum_a);
-          psum_b = __ffma2_rn(e1, make_float2(inv.z, inv.w), psum_b);
-          const float2 b0 = __ffma2_rn(e0, c255, magic2), b1 = __ffma2_rn(e1, c255, magic2);  // low byte = rne(255 e)
-          const uint32_t lo = __byte_perm(__float_as_uint(b0.x), __float_as_uint(b0.y), 0x0040);
-          const uint32_t hi = __byte_perm(__float_as_uint(b1.x), __float_as_uint(b1.y), 0x0040);
-          packed[c4] = __byte_perm(lo, hi, 0x5410);
+        for (int q4 = 0; q4 < 4; ++q4) {
+          const float4 add = vk[kKeyTile / 4 + ch * 4 + q4];
+          const float2 f0 = __fadd2_rn(make_float2(__uint_as_float(sr[q4 * 4 + 0]), __uint_as_float(sr[q4 * 4 + 1])), neg_magic2);
+          const float2 f1 = __fadd2_rn(make_float2(__uint_as_float(sr[q4 * 4 + 2]), __uint_as_float(sr[q4 * 4 + 3])), neg_magic2);
+          if (K_PER_BLOCK) {
+            t2[q4 * 2 + 0] = __ffma2_rn(f0, mt2, make_float2(add.x, add.y));
+            t2[q4 * 2 + 1] = __ffma2_rn(f1, mt2, make_float2(add.z, add.w));
+          } else {
+            const float4 mul = vk[ch * 4 + q4];
+            t2[q4 * 2 + 0] = __ffma2_rn(__fmul2_rn(f0, mt2), make_float2(mul.x, mul.y), make_float2(add.x, add.y));
+            t2[q4 * 2 + 1] = __ffma2_rn(__fmul2_rn(f1, mt2), make_float2(mul.z, mul.w), make_float2(add.z, add.w));
+          }
         }
-        st = make_float2(bm, (psum_a.x + psum_a.y) + (psum_b.x + psum_b.y));
-      } else {
-        const float nm = fmaxf(m_run, bm);
-        const float ns = (nm == -INFINITY) ? 0.f : nm;
-        const float ow = (m_run == nm) ? 1.f : ex2_approx(m_run - ns);
-        const float off = 8.807354922057604f - ns;  // log2(448): P = e4m3(448 * 2^(t - max))
-        const float2 off2 = make_float2(off, off);
-        float2 psum2 = make_float2(0.f, 0.f);
+        if (diag) {
 #pragma unroll
-        for (int c4 = 0; c4 < kKeyTile / 4; ++c4) {
-          const float2 d0 = __fadd2_rn(t2[c4 * 2 + 0], off2), d1 = __fadd2_rn(t2[c4 * 2 + 1], off2);
-          const float2 e0 = make_float2(ex2_approx(d0.x), ex2_approx(d0.y));
-          const float2 e1 = make_float2(ex2_approx(d1.x), ex2_approx(d1.y));
-          psum2 = __fadd2_rn(psum2, __fadd2_rn(e0, e1));
-          const uint32_t lo = __nv_cvt_float2_to_fp8x2(e0, __NV_SATFINITE, __NV_E4M3);
-          const uint32_t hi = __nv_cvt_float2_to_fp8x2(e1, __NV_SATFINITE, __NV_E4M3);
-          packed[c4] = __byte_perm(lo, hi, 0x5410);
+          for (int c2 = 0; c2 < 8; ++c2) {
+            if (ch * 16 + 2 * c2 > lim) t2[c2].x = -INFINITY;
+            if (ch * 16 + 2 * c2 + 1 > lim) t2[c2].y = -INFINITY;
+          }
         }
-        st = make_float2(ow, (psum2.x + psum2.y) * (1.f / 448.f));
-        m_run = nm;
+      };
+
+      // ---- pass 1: tile maximum
+      uint32_t sbuf[2][16];
+      float bm0 = -INFINITY, bm1 = -INFINITY;
+      tmem_ld16(s_addr, sbuf[0]);
+#pragma unroll 1
+      for (int ch = 0; ch < kKeyTile / 16; ch += 2) {
+        float2 t2[8];
+        tmem_wait_ld();
+        tmem_ld16(s_addr + (ch + 1) * 16, sbuf[1]);
+        scores16(sbuf[0], ch, t2);
+#pragma unroll
+        for (int c2 = 0; c2 < 8; c2 += 2) { bm0 = max3(bm0, t2[c2].x, t2[c2].y); bm1 = max3(bm1, t2[c2 + 1].x, t2[c2 + 1].y); }
+        tmem_wait_ld();
+        tmem_ld16(s_addr + ((ch + 2) % (kKeyTile / 16)) * 16, sbuf[0]);  // wraps to chunk 0 for pass 2
+        scores16(sbuf[1], ch + 1, t2);
+#pragma unroll
+        for (int c2 = 0; c2 < 8; c2 += 2) { bm0 = max3(bm0, t2[c2].x, t2[c2].y); bm1 = max3(bm1, t2[c2 + 1].x, t2[c2 + 1].y); }
       }
-      }
+      const float bm = fmaxf(bm0, bm1);
+      if ((warp & 3) == 0) PK_TRACE_AT(wg, j, 2);
+
       // probability buffer j%NP was last read by the PV product of tile j-NP
       if (j >= NP && !__all_sync(0xffffffffu, mbar_wait_bounded(bars.pv_done(j % NP), ((j / NP) - 1) & 1, abort_flag, W_SM_PV))) break;
       tc_fence_after();
-      tmem_st16(lane_addr + C::COL_P + (j % NP) * (kKeyTile / 4), packed);
-      tmem_wait_st();
-      stat_ring[(j % NSTAT) * kQTile + row] = st;
-      if (dumping && j == 0) {
-        uint32_t* dp = reinterpret_cast<uint32_t*>(static_cast<char*>(prm.dump) + kQTile * kKeyTile * 4);
-#pragma unroll
-        for (int c = 0; c < kKeyTile / 4; ++c) dp[row * (kKeyTile / 4) + c] = packed[c];
+      const uint32_t p_addr = lane_addr + C::COL_P + (j % NP) * (kKeyTile / 4);
+
+      // ---- pass 2: probabilities, 8-bit codes, denominator term
+      float shift, ow = 1.f;
+      if (ALGO == kPiper) {
+        shift = (bm == -INFINITY) ? 0.f : -bm;
+      } else {
+        const float nm = fmaxf(m_run, bm);
+        const float ns = (nm == -INFINITY) ? 0.f : nm;
+        ow = (m_run == nm) ? 1.f : ex2_approx(m_run - ns);
+        shift = 8.807354922057604f - ns;  // log2(448): P = e4m3(448 * 2^(t - max))
+        m_run = nm;
       }
+      const float2 shift2 = make_float2(shift, shift);
+      const float2 c255 = make_float2(255.f, 255.f), magic2 = make_float2(kMagic, kMagic);
+      float2 psum_a = make_float2(0.f, 0.f), psum_b = make_float2(0.f, 0.f);
+      auto probs16 = [&](const uint32_t* sr, int ch) {
+        float2 t2[8];
+        scores16(sr, ch, t2);
+        uint32_t pk[4];
+#pragma unroll
+        for (int q4 = 0; q4 < 4; ++q4) {
+          const float2 d0 = __fadd2_rn(t2[q4 * 2 + 0], shift2), d1 = __fadd2_rn(t2[q4 * 2 + 1], shift2);
+          const float2 e0 = make_float2(ex2_approx(d0.x), ex2_approx(d0.y));
+          const float2 e1 = make_float2(ex2_approx(d1.x), ex2_approx(d1.y));
+          if (ALGO == kPiper) {
+            const float4 inv = vk[2 * (kKeyTile / 4) + ch * 4 + q4];
+            psum_a = __ffma2_rn(e0, make_float2(inv.x, inv.y), psum_a);
+            psum_b = __ffma2_rn(e1, make_float2(inv.z, inv.w), psum_b);
+            const float2 b0 = __ffma2_rn(e0, c255, magic2), b1 = __ffma2_rn(e1, c255, magic2);  // low byte = rne(255 e)
+            const uint32_t lo = __byte_perm(__float_as_uint(b0.x), __float_as_uint(b0.y), 0x0040);
+            const uint32_t hi = __byte_perm(__float_as_uint(b1.x), __float_as_uint(b1.y), 0x0040);
+            pk[q4] = __byte_perm(lo, hi, 0x5410);
+          } else {
+            psum_a = __fadd2_rn(psum_a, e0);
+            psum_b = __fadd2_rn(psum_b, e1);
+            const uint32_t lo = __nv_cvt_float2_to_fp8x2(e0, __NV_SATFINITE, __NV_E4M3);
+            const uint32_t hi = __nv_cvt_float2_to_fp8x2(e1, __NV_SATFINITE, __NV_E4M3);
+            pk[q4] = __byte_perm(lo, hi, 0x5410);
+          }
+        }
+        tmem_st4(p_addr + ch * 4, pk);
+        if (DUMP) {
+          if (dumping && j == 0) {
+            int32_t* ds = static_cast<int32_t*>(prm.dump);
+            uint32_t* dp = reinterpret_cast<uint32_t*>(static_cast<char*>(prm.dump) + kQTile * kKeyTile * 4);
+#pragma unroll
+            for (int c = 0; c < 16; ++c) ds[row * kKeyTile + ch * 16 + c] = static_cast<int32_t>(sr[c] - kMagicBits);
+#pragma unroll
+            for (int c = 0; c < 4; ++c) dp[row * (kKeyTile / 4) + ch * 4 + c] = pk[c];
+          }
+        }
+      };
+#pragma unroll 1
+      for (int ch = 0; ch < kKeyTile / 16; ch += 2) {
+        tmem_wait_ld();
+        tmem_ld16(s_addr + (ch + 1) * 16, sbuf[1]);
+        probs16(sbuf[0], ch);
+        tmem_wait_ld();
+        if (ch + 2 < kKeyTile / 16) tmem_ld16(s_addr + (ch + 2) * 16, sbuf[0]);
+        probs16(sbuf[1], ch + 1);
+      }
+      // hand the score buffer back re-armed, publish the probabilities and the row statistics
+      tmem_arm(s_addr, kKeyTile);
+      const float psum = (psum_a.x + psum_a.y) + (psum_b.x + psum_b.y);
+      const float2 st = (ALGO == kPiper) ? make_float2(bm, psum) : make_float2(ow, psum * (1.f / 448.f));
+      stat_ring[(j % NSTAT) * kQTile + row] = st;
+      tmem_wait_st();
       tc_fence_before();
+      mbar_arrive(bars.s_free(j % NS));
       mbar_arrive(bars.p_ready(j % NP));
       mbar_arrive(bars.stat_full(j % NSTAT));
       if ((warp & 3) == 0) PK_TRACE_AT(wg, j, 3);
     }
   } else if (wg == NSWG) {
     // ------------------------------------------------------------------ dequant + epilogue
-    if (NSWG == 2) setmaxnreg_inc<216>(); else setmaxnreg_inc<216>();
+    if (NSWG == 2) setmaxnreg_inc<232>(); else setmaxnreg_inc<232>();
     const int row = tid & 127;
     const uint32_t lane_addr = tmem_base + (static_cast<uint32_t>((warp & 3) * 32) << 16);
     if (O_MAGIC) {
@@ -493,7 +521,7 @@ fused_attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
         if (ch + 1 < D / 16) tmem_ld16(o_addr + (ch + 1) * 16, obuf[(ch + 1) & 1]);
         if (O_MAGIC) tmem_arm(o_addr + ch * 16, 16);
         const uint32_t* o = obuf[ch & 1];
-        if (dumping && j == 0) {
+        if (DUMP && dumping && j == 0) {
           uint32_t* dp = reinterpret_cast<uint32_t*>(static_cast<char*>(prm.dump) + kQTile * kKeyTile * 5);
 #pragma unroll
           for (int i = 0; i < 16; ++i) dp[row * D + ch * 16 + i] = O_MAGIC ? o[i] - kMagicBits : o[i];
@@ -522,7 +550,9 @@ fused_attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
     // epilogue: normalise, restore the V mean (piper) / apply the channel scale (sage), cast
     const int grow = q0 + row;
     if (ok && grow < prm.Sq) {
-      const float dmax = fmaxf(den, 1e-30f);
+      // one IEEE division per row; the D per-element divisions of the reference become
+      // multiplications by the reciprocal (at most an ulp apart, and far less code)
+      const float dinv = __fdiv_rn(1.f, fmaxf(den, 1e-30f));
       const float* aux = prm.v_aux + static_cast<long long>(bh) * D;
       const long long obase = (static_cast<long long>(bh) * prm.Sq + grow) * D;
 #pragma unroll
@@ -531,8 +561,8 @@ fused_attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
 #pragma unroll
         for (int i = 0; i < 8; ++i) {
           const float nv = (i & 1) ? num2[(d0 + i) / 2].y : num2[(d0 + i) / 2].x;
-          if (ALGO == kPiper) r[i] = __fdiv_rn(nv, dmax) + aux[d0 + i];
-          else r[i] = __fdiv_rn(nv * __fdiv_rn(aux[d0 + i], 448.f), dmax);
+          if (ALGO == kPiper) r[i] = fmaf(nv, dinv, aux[d0 + i]);
+          else r[i] = nv * (aux[d0 + i] * (1.f / 448.f)) * dinv;
         }
         if (prm.out_dtype == PK_F32) {
           float4* o = reinterpret_cast<float4*>(static_cast<float*>(prm.out) + obase + d0);
@@ -600,8 +630,8 @@ int make_map(CUtensorMap* m, void* base, uint64_t rows, uint64_t cols, uint32_t 
   return PK_OK;
 }
 
-template <int D, int ALGO, bool KPB>
-int launch_one(const pk_problem& p, const Layout& L, cudaStream_t st, const DebugDump* dump) {
+template <int D, int ALGO, bool KPB, bool DUMP>
+int launch_one_impl(const pk_problem& p, const Layout& L, cudaStream_t st, const DebugDump* dump) {
   using C = Cfg<D, ALGO>;
   CUtensorMap tq, tk, tv;
   int rc;
@@ -626,7 +656,7 @@ int launch_one(const pk_problem& p, const Layout& L, cudaStream_t st, const Debu
 #ifdef PK_TRACE
   if (const char* a = getenv("PK_ABLATE")) prm.ablate = atoi(a);
 #endif
-  auto kern = fused_attention_kernel<D, ALGO, KPB>;
+  auto kern = fused_attention_kernel<D, ALGO, KPB, DUMP>;
   {
     const cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES);
     if (e != cudaSuccess) return fail(PK_ERR_CUDA, "cudaFuncSetAttribute: %s", cuda_err(e));
@@ -636,6 +666,11 @@ int launch_one(const pk_problem& p, const Layout& L, cudaStream_t st, const Debu
   const cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return fail(PK_ERR_CUDA, "fused kernel launch failed: %s", cuda_err(e));
   return PK_OK;
+}
+
+template <int D, int ALGO, bool KPB>
+int launch_one(const pk_problem& p, const Layout& L, cudaStream_t st, const DebugDump* dump) {
+  return dump ? launch_one_impl<D, ALGO, KPB, true>(p, L, st, dump) : launch_one_impl<D, ALGO, KPB, false>(p, L, st, dump);
 }
 
 template <int D, int ALGO>

@@ -57,18 +57,14 @@ __device__ __forceinline__ bool mbar_test_wait(uint32_t bar, uint32_t parity) {
 // Wait limit: ~1.5e9 SM cycles (well under a second at any clock this part runs at).
 constexpr long long kWaitCycleLimit = 1500000000LL;
 
-// Returns false when the wait was abandoned (time limit, or another thread already raised
-// *abort_flag).  On a time-out the caller's `where` code is stored into *abort_flag.
-__device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity,
-                                                  volatile int* abort_flag, int where) {
-  if (mbar_try_wait(bar, parity)) return true;
+// Slow path of a wait (inlined: an out-of-line call cannot be shared by roles that run with
+// different register allocations).
+__device__ __forceinline__ bool mbar_wait_slow(uint32_t bar, uint32_t parity, volatile int* abort_flag,
+                                            int where) {
   const long long t0 = clock64();
   uint32_t polls = 0;
   while (true) {
     if (mbar_try_wait(bar, parity)) return true;
-#ifdef PK_WAIT_SLEEP
-    __nanosleep(PK_WAIT_SLEEP);
-#endif
     if ((++polls & 0x3FF) == 0) {
       if (*abort_flag != 0) return false;
       if (clock64() - t0 > kWaitCycleLimit) {
@@ -77,6 +73,14 @@ __device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity,
       }
     }
   }
+}
+
+// Returns false when the wait was abandoned (time limit, or another thread already raised
+// *abort_flag).  On a time-out the caller's `where` code is stored into *abort_flag.
+__device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity,
+                                                  volatile int* abort_flag, int where) {
+  if (mbar_try_wait(bar, parity)) return true;
+  return mbar_wait_slow(bar, parity, abort_flag, where);
 }
 
 __device__ __forceinline__ void fence_barrier_init() {
@@ -176,6 +180,12 @@ __device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t* r) {
       "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]),
       "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
       : "memory");
+}
+
+__device__ __forceinline__ void tmem_st4(uint32_t taddr, const uint32_t* r) {
+  asm volatile("tcgen05.st.sync.aligned.32x32b.x4.b32 [%0], {%1,%2,%3,%4};" ::"r"(taddr), "r"(r[0]),
+               "r"(r[1]), "r"(r[2]), "r"(r[3])
+               : "memory");
 }
 
 // ---------------------------------------------------------------------------------------
