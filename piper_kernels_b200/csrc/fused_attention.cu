@@ -336,6 +336,13 @@ fused_attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
       // t_c = score_c * (q_mul * k_mul_c) + k_add_c for the 16 columns of chunk `ch`, two columns
       // per packed FP32 instruction; the word read from tensor memory is the float 1.5*2^23 + score.
       auto scores16 = [&](const uint32_t* sr, int ch, float2* t2) {
+        if (DUMP) {
+          if (dumping && j == 0) {
+            int32_t* ds = static_cast<int32_t*>(prm.dump);
+#pragma unroll
+            for (int c = 0; c < 16; ++c) ds[row * kKeyTile + ch * 16 + c] = static_cast<int32_t>(sr[c] - kMagicBits);
+          }
+        }
 #pragma unroll
         for (int q4 = 0; q4 < 4; ++q4) {
           const float4 add = vk[kKeyTile / 4 + ch * 4 + q4];
@@ -369,14 +376,18 @@ fused_attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
         tmem_wait_ld();
         tmem_ld16(s_addr + (ch + 1) * 16, sbuf[1]);
         scores16(sbuf[0], ch, t2);
+        tmem_st16(s_addr + ch * 16, reinterpret_cast<const uint32_t*>(t2));  // pass 2 reads t, not the raw score
 #pragma unroll
         for (int c2 = 0; c2 < 8; c2 += 2) { bm0 = max3(bm0, t2[c2].x, t2[c2].y); bm1 = max3(bm1, t2[c2 + 1].x, t2[c2 + 1].y); }
         tmem_wait_ld();
-        tmem_ld16(s_addr + ((ch + 2) % (kKeyTile / 16)) * 16, sbuf[0]);  // wraps to chunk 0 for pass 2
+        if (ch + 2 < kKeyTile / 16) tmem_ld16(s_addr + (ch + 2) * 16, sbuf[0]);
         scores16(sbuf[1], ch + 1, t2);
+        tmem_st16(s_addr + (ch + 1) * 16, reinterpret_cast<const uint32_t*>(t2));
 #pragma unroll
         for (int c2 = 0; c2 < 8; c2 += 2) { bm0 = max3(bm0, t2[c2].x, t2[c2].y); bm1 = max3(bm1, t2[c2 + 1].x, t2[c2 + 1].y); }
       }
+      tmem_wait_st();
+      tmem_ld16(s_addr, sbuf[0]);  // first chunk of pass 2
       const float bm = fmaxf(bm0, bm1);
       if ((warp & 3) == 0) PK_TRACE_AT(wg, j, 2);
 
@@ -400,8 +411,7 @@ fused_attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
       const float2 c255 = make_float2(255.f, 255.f), magic2 = make_float2(kMagic, kMagic);
       float2 psum_a = make_float2(0.f, 0.f), psum_b = make_float2(0.f, 0.f);
       auto probs16 = [&](const uint32_t* sr, int ch) {
-        float2 t2[8];
-        scores16(sr, ch, t2);
+        const float2* t2 = reinterpret_cast<const float2*>(sr);
         uint32_t pk[4];
 #pragma unroll
         for (int q4 = 0; q4 < 4; ++q4) {
@@ -427,10 +437,7 @@ fused_attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
         tmem_st4(p_addr + ch * 4, pk);
         if (DUMP) {
           if (dumping && j == 0) {
-            int32_t* ds = static_cast<int32_t*>(prm.dump);
             uint32_t* dp = reinterpret_cast<uint32_t*>(static_cast<char*>(prm.dump) + kQTile * kKeyTile * 4);
-#pragma unroll
-            for (int c = 0; c < 16; ++c) ds[row * kKeyTile + ch * 16 + c] = static_cast<int32_t>(sr[c] - kMagicBits);
 #pragma unroll
             for (int c = 0; c < 4; ++c) dp[row * (kKeyTile / 4) + ch * 4 + c] = pk[c];
           }

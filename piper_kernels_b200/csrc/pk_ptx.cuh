@@ -41,6 +41,21 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
   return ok != 0;
 }
 
+// Same probe, but the hardware may keep the thread suspended for up to `ns` nanoseconds while the
+// phase is incomplete (it resumes as soon as the phase completes), so a waiting warp spends
+// few issue slots on polling.
+__device__ __forceinline__ bool mbar_try_wait_hint(uint32_t bar, uint32_t parity, uint32_t ns) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity), "r"(ns)
+      : "memory");
+  return ok != 0;
+}
+
 // Non-blocking probe of a phase (used where one thread polls several barriers).
 __device__ __forceinline__ bool mbar_test_wait(uint32_t bar, uint32_t parity) {
   uint32_t ok;
@@ -64,8 +79,8 @@ __device__ __forceinline__ bool mbar_wait_slow(uint32_t bar, uint32_t parity, vo
   const long long t0 = clock64();
   uint32_t polls = 0;
   while (true) {
-    if (mbar_try_wait(bar, parity)) return true;
-    if ((++polls & 0x3FF) == 0) {
+    if (mbar_try_wait_hint(bar, parity, 20000u)) return true;
+    if ((++polls & 0x3F) == 0) {
       if (*abort_flag != 0) return false;
       if (clock64() - t0 > kWaitCycleLimit) {
         *abort_flag = where;
