@@ -122,6 +122,23 @@ PK_API int pk_device_status(const pk_problem* p, int32_t status[16]);
  * head `bh` into `dump` (device memory, 128*64*4 + 128*64 + 128*head_dim*4 bytes). */
 PK_API int pk_debug_first_tile(const pk_problem* p, int sage, int bh, int q_tile, void* dump);
 
+/* K and V sequence means ([batch*heads, head_dim] f32 each, device memory) computed without a
+ * workspace and without any allocation.  No counterpart in the reference: it exists for hosts
+ * that cannot allocate device memory where they call the library (a frozen memory pool, a
+ * runtime that hands a plug-in fixed buffers, an allocator whose state is being recorded).
+ * The FP64 partial sums live in an 8 MiB array inside the library image, held by every device
+ * that loads the library until the process exits.
+ *   - Limit: batch*heads*ceil(kv_len/512)*head_dim <= 524288; larger problems are rejected with
+ *     PK_ERR_BAD_ARG (use pk_piper_prepare with a workspace).
+ *   - Only q-independent fields of `p` are used: batch, heads, kv_len, head_dim, in_dtype, k, v,
+ *     their strides, device, stream (q_len/q/scale must still be valid).
+ *   - The first call on a device looks up the array's device address; make that call before
+ *     starting a stream capture.
+ *   - All calls share the one array: calls that may overlap on the GPU (different streams) race.
+ *     Nothing needs clearing between calls: each call overwrites every partial it reads.
+ * Results are bit-identical to the k_mean / v_mean views of pk_piper_prepare with center_value=1. */
+PK_API int pk_kv_means_static(const pk_problem* p, float* k_mean, float* v_mean);
+
 #ifdef __cplusplus
 }
 #endif

@@ -237,6 +237,17 @@ PK_API int pk_device_status(const pk_problem* p, int32_t status[16]) {
   return PK_OK;
 }
 
+PK_API int pk_kv_means_static(const pk_problem* p, float* k_mean, float* v_mean) {
+  g_err[0] = 0;
+  int rc = validate(p, kPiper, false);
+  if (rc) return rc;
+  if (!k_mean || !v_mean) return fail(PK_ERR_BAD_ARG, "pk_kv_means_static: null output pointer");
+  DeviceGuard g(p->device);
+  if (g.err != cudaSuccess) return fail(PK_ERR_CUDA, "cudaSetDevice(%d): %s", p->device, cuda_err(g.err));
+  if ((rc = check_arch(p))) return rc;
+  return kv_means_static(*p, k_mean, v_mean);
+}
+
 PK_API int pk_debug_first_tile(const pk_problem* p, int sage, int bh, int q_tile, void* dump) {
   if (!dump) return fail(PK_ERR_BAD_ARG, "pk_debug_first_tile: null dump pointer");
   const DebugDump d{dump, bh, q_tile};

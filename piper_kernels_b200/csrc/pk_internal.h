@@ -36,6 +36,10 @@ int validate(const pk_problem* p, Algo algo, bool need_workspace);
 // Prepass launchers (prepass.cu).  All asynchronous on `stream`.
 int launch_prepass(const pk_problem& p, const Layout& L, Algo algo, cudaStream_t stream);
 
+// K and V sequence means with the partial sums in the library's own static device array
+// (prepass.cu).  The caller has validated `p` and made p.device current.
+int kv_means_static(const pk_problem& p, float* k_mean, float* v_mean);
+
 // Fused kernels (fused_attention.cu).
 struct DebugDump {
   void* ptr;

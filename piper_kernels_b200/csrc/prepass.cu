@@ -545,4 +545,75 @@ int launch_prepass(const pk_problem& p, const Layout& L, Algo algo, cudaStream_t
                            : run_prepass_a<__nv_bfloat16, 64>(p, L, algo, st);
 }
 
+// ---------------------------------------------------------------------------------------
+// K / V sequence means without any caller-provided scratch.
+//
+// Some hosts that embed this library may not allocate device memory at the point where they
+// need the means: code running under a memory pool that has been frozen for the lifetime of a
+// serving process, plug-ins that are handed fixed input/output buffers by their runtime, or
+// callers that must not disturb an allocator whose state is being recorded.  For them the
+// per-chunk FP64 partial sums live in a fixed array inside the library image instead of in a
+// workspace.  Every device that loads the library carries the array (8 MiB) until exit.
+// ---------------------------------------------------------------------------------------
+namespace {
+
+constexpr long long kStaticPartialsPerTensor = 512 * 1024;  // FP64 words: batch*heads*ceil(kv_len/512)*head_dim
+static __device__ __align__(256) double g_static_mean_partials[2 * kStaticPartialsPerTensor];
+
+// Device address of the array, looked up once per device while that device is current.  The
+// array's name in host code is only a handle for this lookup, never a pointer to pass along.
+double* static_partials_for_current_device(int device, cudaError_t* err) {
+  static double* cache[64] = {};
+  if (device >= 0 && device < 64 && cache[device] != nullptr) {
+    *err = cudaSuccess;
+    return cache[device];
+  }
+  double* ptr = nullptr;
+  *err = cudaGetSymbolAddress(reinterpret_cast<void**>(&ptr), g_static_mean_partials);
+  if (*err != cudaSuccess) return nullptr;
+  if (device >= 0 && device < 64) cache[device] = ptr;
+  return ptr;
+}
+
+template <typename T, int D>
+void launch_means_static(const pk_problem& p, double* scratch, float* k_mean, float* v_mean, int chunks,
+                         cudaStream_t st) {
+  const TensorArg k{p.k, p.k_stride[0], p.k_stride[1], p.k_stride[2]};
+  const TensorArg v{p.v, p.v_stride[0], p.v_stride[1], p.v_stride[2]};
+  const int BH = p.batch * p.heads;
+  double* k_part = scratch;
+  double* v_part = scratch + kStaticPartialsPerTensor;
+  const bool al = aligned16(p.k, p.k_stride, 2) && aligned16(p.v, p.v_stride, 2);
+  // Each launch overwrites every partial it later reads, so nothing needs clearing first.
+  if (al) colstat_partial_kernel<T, D, true><<<dim3(chunks, BH), kThreads, 0, st>>>(k, v, k_part, v_part, p.kv_len, p.heads, chunks, 1, 1);
+  else colstat_partial_kernel<T, D, false><<<dim3(chunks, BH), kThreads, 0, st>>>(k, v, k_part, v_part, p.kv_len, p.heads, chunks, 1, 1);
+  colstat_finalize_kernel<<<BH, D, 0, st>>>(k_part, v_part, nullptr, nullptr, k_mean, v_mean, p.kv_len, D, chunks, 1);
+}
+
+}  // namespace
+
+int kv_means_static(const pk_problem& p, float* k_mean, float* v_mean) {
+  const int chunks = (p.kv_len + kStatChunkRows - 1) / kStatChunkRows;
+  const long long need = static_cast<long long>(p.batch) * p.heads * chunks * p.head_dim;
+  if (need > kStaticPartialsPerTensor)
+    return fail(PK_ERR_BAD_ARG,
+                "pk_kv_means_static: batch*heads*ceil(kv_len/512)*head_dim = %lld exceeds the built-in scratch of %lld "
+                "partial sums; use pk_piper_prepare with a workspace instead",
+                need, kStaticPartialsPerTensor);
+  cudaError_t e;
+  double* scratch = static_partials_for_current_device(p.device, &e);
+  if (!scratch) return fail(PK_ERR_CUDA, "pk_kv_means_static: cudaGetSymbolAddress failed: %s", cuda_err(e));
+  cudaStream_t st = static_cast<cudaStream_t>(p.stream);
+  if (p.in_dtype == PK_F16) {
+    if (p.head_dim == 128) launch_means_static<__half, 128>(p, scratch, k_mean, v_mean, chunks, st);
+    else launch_means_static<__half, 64>(p, scratch, k_mean, v_mean, chunks, st);
+  } else {
+    if (p.head_dim == 128) launch_means_static<__nv_bfloat16, 128>(p, scratch, k_mean, v_mean, chunks, st);
+    else launch_means_static<__nv_bfloat16, 64>(p, scratch, k_mean, v_mean, chunks, st);
+  }
+  e = cudaGetLastError();
+  if (e != cudaSuccess) return fail(PK_ERR_CUDA, "pk_kv_means_static launch failed: %s", cuda_err(e));
+  return PK_OK;
+}
+
 }  // namespace pk
