@@ -122,6 +122,12 @@ PK_API int pk_device_status(const pk_problem* p, int32_t status[16]);
  * head `bh` into `dump` (device memory, 128*64*4 + 128*64 + 128*head_dim*4 bytes). */
 PK_API int pk_debug_first_tile(const pk_problem* p, int sage, int bh, int q_tile, void* dump);
 
+/* Profiling aid: runs the ordinary fused kernel and records, for the CTA of query tile `q_tile`
+ * of flattened head `bh`, clock64() stamps of every warp role per key tile into `stamps`
+ * (device memory, int64 [6 roles][max_tiles][8]; roles: 0/1 softmax warpgroups, 2 dequant,
+ * 3 S-product issue, 4 PV-product issue, 5 producer). */
+PK_API int pk_debug_timeline(const pk_problem* p, int sage, int bh, int q_tile, void* stamps, int max_tiles);
+
 /* K and V sequence means ([batch*heads, head_dim] f32 each, device memory) computed without a
  * workspace and without any allocation.  No counterpart in the reference: it exists for hosts
  * that cannot allocate device memory where they call the library (a frozen memory pool, a

@@ -20,7 +20,7 @@ EXPORTS = (
     "pk_version", "pk_last_error",
     "pk_piper_workspace_bytes", "pk_piper_prepare", "pk_piper_run", "pk_piper_attention_fwd",
     "pk_sage2pp_workspace_bytes", "pk_sage2pp_prepare", "pk_sage2pp_run", "pk_sage2pp_attention_fwd",
-    "pk_device_status", "pk_debug_first_tile", "pk_kv_means_static",
+    "pk_device_status", "pk_debug_first_tile", "pk_kv_means_static", "pk_debug_timeline",
 )
 
 
@@ -79,6 +79,7 @@ def lib() -> C.CDLL:
             getattr(handle, name).argtypes = [P]
         handle.pk_device_status.argtypes = [P, C.POINTER(C.c_int32 * 16)]
         handle.pk_debug_first_tile.argtypes = [P, C.c_int, C.c_int, C.c_int, C.c_void_p]
+        handle.pk_debug_timeline.argtypes = [P, C.c_int, C.c_int, C.c_int, C.c_void_p, C.c_int]
         handle.pk_kv_means_static.argtypes = [P, C.c_void_p, C.c_void_p]
         for name in EXPORTS[2:]:
             getattr(handle, name).restype = C.c_int

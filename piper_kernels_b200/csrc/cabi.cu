@@ -250,7 +250,13 @@ PK_API int pk_kv_means_static(const pk_problem* p, float* k_mean, float* v_mean)
 
 PK_API int pk_debug_first_tile(const pk_problem* p, int sage, int bh, int q_tile, void* dump) {
   if (!dump) return fail(PK_ERR_BAD_ARG, "pk_debug_first_tile: null dump pointer");
-  const DebugDump d{dump, bh, q_tile};
+  const DebugDump d{dump, bh, q_tile, nullptr, 0};
+  return run(p, sage ? kSage : kPiper, &d);
+}
+
+PK_API int pk_debug_timeline(const pk_problem* p, int sage, int bh, int q_tile, void* stamps, int max_tiles) {
+  if (!stamps || max_tiles <= 0) return fail(PK_ERR_BAD_ARG, "pk_debug_timeline: null buffer");
+  const DebugDump d{nullptr, bh, q_tile, stamps, max_tiles};
   return run(p, sage ? kSage : kPiper, &d);
 }
 

@@ -33,10 +33,25 @@
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 #include <cuda_fp8.h>
-#include <stdlib.h>
 
 #include "pk_internal.h"
 #include "pk_ptx.cuh"
+
+#ifndef PK_SOFTMAX_UNROLLED
+#define PK_SOFTMAX_UNROLLED 1
+#endif
+#ifndef PK_NDQ
+#define PK_NDQ 1
+#endif
+#ifndef PK_NSWG_PIPER
+#define PK_NSWG_PIPER 2
+#endif
+// per-role register allocations (piper): softmax, dequant, helper warpgroups
+#ifndef PK_REG_SM
+#define PK_REG_SM 112
+#define PK_REG_DQ 232
+#define PK_REG_HELPER 56
+#endif
 
 namespace pk {
 namespace {
@@ -67,13 +82,16 @@ struct FusedParams {
   int32_t* status;
   void* dump;
   int dump_bh, dump_qt;
-  int ablate;  // development builds only (-DPK_TRACE): 1 skips the softmax math, 2 the dequant math
+  long long* timeline;  // optional [6][timeline_tiles][4] clock stamps of CTA (dump_bh, dump_qt)
+  int timeline_tiles;
 };
 
 template <int D, int ALGO>
 struct Cfg {
-  static constexpr int NSWG = (ALGO == kPiper) ? 2 : 1;
-  static constexpr int THREADS = (NSWG + 2) * 128;
+  static constexpr int NSWG = (ALGO == kPiper) ? PK_NSWG_PIPER : 1;
+  static constexpr int NDQ = PK_NDQ;  // dequant warpgroups; each folds D / NDQ columns of every partial
+  static constexpr int THREADS = (NSWG + NDQ + 1) * 128;
+  static constexpr int LAUNCH_REGS = (65536 / THREADS) / 8 * 8;  // registers per thread at launch
   static constexpr int Q_BYTES = kQTile * D;
   static constexpr int K_BYTES = kKeyTile * D;
   static constexpr int V_BYTES = D * kKeyTile;
@@ -118,17 +136,15 @@ enum : int {
   W_SM_VEC = 31, W_SM_S = 32, W_SM_PV = 33, W_DQ_STAT = 41, W_DQ_O = 42
 };
 
-// Optional per-role timestamps of one CTA (development builds only: -DPK_TRACE).  Written to
-// the debug dump buffer at byte offset 256 KiB as int64 [role][tile][4], six roles.
-#ifdef PK_TRACE
-#define PK_TRACE_AT(role, tile, k)                                                                   \
+// Per-role timeline of one CTA for pk_debug_timeline(): int64 clock64() stamps laid out
+// [role][tile][8], roles: 0/1 softmax warpgroups, 2 dequant, 3 S-product issue, 4 PV-product
+// issue, 5 producer.  One thread per role stamps; other CTAs and ordinary launches skip it.
+constexpr int kTimelineRoles = 6;
+#define PK_STAMP(role, tile, k)                                                                     \
   do {                                                                                               \
-    if (dumping && (tile) < 1024 && (threadIdx.x & 31) == 0)                                          \
-      reinterpret_cast<long long*>(static_cast<char*>(prm.dump) + (256 << 10))[((role) * 1024 + (tile)) * 4 + (k)] = clock64(); \
+    if (TIMELINE && stamping && (tile) < prm.timeline_tiles)                                         \
+      prm.timeline[(static_cast<long long>(role) * prm.timeline_tiles + (tile)) * 8 + (k)] = clock64(); \
   } while (0)
-#else
-#define PK_TRACE_AT(role, tile, k) do { } while (0)
-#endif
 
 __device__ __forceinline__ float max3(float a, float b, float c) {
   float r;
@@ -144,12 +160,14 @@ __device__ __forceinline__ void tmem_arm(uint32_t addr, int ncols) {
   for (int c = 0; c < ncols; c += 16) tmem_st16(addr + c, m);
 }
 
-template <int D, int ALGO, bool K_PER_BLOCK, bool DUMP>
+template <int D, int ALGO, bool K_PER_BLOCK, int DEBUG>
 __global__ void __launch_bounds__(Cfg<D, ALGO>::THREADS, 1)
 fused_attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                        const __grid_constant__ CUtensorMap tm_v, const FusedParams prm) {
   using C = Cfg<D, ALGO>;
   constexpr int NSWG = C::NSWG;
+  constexpr bool DUMP = DEBUG == 1;      // copy out the first key tile's intermediates
+  constexpr bool TIMELINE = DEBUG == 2;  // per-role clock stamps of one CTA
 #ifdef PK_NO_O_MAGIC
   constexpr bool O_MAGIC = false;
 #else
@@ -173,6 +191,8 @@ fused_attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
   const int n_tiles = prm.causal ? min(n_all, 2 * qt + 2) : n_all;
   // DUMP instantiations (debug entry point only) copy the first key tile's intermediates out
   const bool dumping = DUMP && prm.dump != nullptr && bh == prm.dump_bh && qt == prm.dump_qt;
+  const bool stamping = TIMELINE && prm.timeline != nullptr && bh == prm.dump_bh && qt == prm.dump_qt &&
+                        ((tid & 127) == 0 || (lane == 0 && wg == NSWG + C::NDQ));
 
   if (tid == 0) {
     mbar_init(bars.q_full(), 1);
@@ -181,12 +201,12 @@ fused_attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
     for (int i = 0; i < NVEC; ++i) mbar_init(bars.vec_full(i), 1);
     for (int i = 0; i < NS; ++i) mbar_init(bars.s_free(i), 128);
     for (int i = 0; i < NP; ++i) { mbar_init(bars.p_ready(i), 128); mbar_init(bars.pv_done(i), 1); }
-    for (int i = 0; i < NO; ++i) mbar_init(bars.o_empty(i), 128);
+    for (int i = 0; i < NO; ++i) mbar_init(bars.o_empty(i), 128 * C::NDQ);
     for (int i = 0; i < NSTAT; ++i) mbar_init(bars.stat_full(i), 128);
     *abort_flag = 0;
     fence_barrier_init();
   }
-  constexpr int PROD_WARP = (NSWG + 1) * 4;
+  constexpr int PROD_WARP = (NSWG + C::NDQ) * 4;
   constexpr int QK_WARP = PROD_WARP + 1;
   constexpr int PV_WARP = PROD_WARP + 2;
   if (warp == PROD_WARP) {
@@ -201,7 +221,7 @@ fused_attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
   // The CTA starts with 128 (piper, 512 threads) or 168 (sage, 384 threads) registers per
   // thread; the dequant rows need more and the helper warpgroup far fewer, so each role
   // resizes its allocation on entry.
-  if (wg == NSWG + 1) setmaxnreg_dec<56>();
+  if (wg == NSWG + C::NDQ) setmaxnreg_dec<(ALGO == kPiper ? PK_REG_HELPER : 48)>();
 
   if (warp == PROD_WARP) {
     // ------------------------------------------------------------------ producer
@@ -214,12 +234,6 @@ fused_attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
         if (i < n_tiles) {
           const int s = i % NK;
           if (i >= NK && !mbar_wait_bounded(bars.qk_done(s), ((i / NK) - 1) & 1, abort_flag, W_PROD_K)) break;
-#ifdef PK_TRACE
-          if ((prm.ablate & 4) && i >= NVEC) {  // development: re-use stale tiles instead of loading
-            mbar_arrive(bars.k_full(s));
-            mbar_arrive(bars.vec_full(i % NVEC));
-          } else
-#endif
           {
           mbar_expect_tx(bars.k_full(s), C::K_BYTES);
           tma_load_2d(smem_base + C::OFF_K + s * C::K_BYTES, &tm_k, bars.k_full(s), 0,
@@ -240,10 +254,6 @@ fused_attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
         if (j >= 0 && j < n_tiles) {
           const int s = j % NV;
           if (j >= NV && !mbar_wait_bounded(bars.pv_done(s), ((j / NV) - 1) & 1, abort_flag, W_PROD_V)) break;
-#ifdef PK_TRACE
-          if ((prm.ablate & 4) && j >= NV) mbar_arrive(bars.v_full(s));
-          else
-#endif
           {
             mbar_expect_tx(bars.v_full(s), C::V_BYTES);
             tma_load_2d(smem_base + C::OFF_V + s * C::V_BYTES, &tm_v, bars.v_full(s), j * kKeyTile, bh * D);
@@ -262,17 +272,17 @@ fused_attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
       const uint64_t kdesc0 = umma_smem_desc(smem_base + C::OFF_K, D);
       bool ok = mbar_wait_bounded(bars.q_full(), 0, abort_flag, W_QK_Q);
       for (int j = 0; ok && j < n_tiles; ++j) {
-        PK_TRACE_AT(3, j, 0);
+        PK_STAMP(3, j, 0);
         if (!mbar_wait_bounded(bars.k_full(j % NK), (j / NK) & 1, abort_flag, W_QK_K)) break;
         if (!mbar_wait_bounded(bars.s_free(j % NS), (j / NS) & 1, abort_flag, W_QK_S)) break;
         tc_fence_after();
-        PK_TRACE_AT(3, j, 1);
+        PK_STAMP(3, j, 1);
         const uint64_t kdesc = kdesc0 + static_cast<uint64_t>(((j % NK) * C::K_BYTES) >> 4);
         const uint32_t d = tmem_base + C::COL_S + (j % NS) * kKeyTile;
 #pragma unroll
         for (int kk = 0; kk < D / 32; ++kk) umma_i8_ss(d, qdesc + 2 * kk, kdesc + 2 * kk, idesc_qk, 1u);
         tc_commit(bars.qk_done(j % NK));
-        PK_TRACE_AT(3, j, 2);
+        PK_STAMP(3, j, 2);
       }
     }
   } else if (warp == PV_WARP) {
@@ -282,12 +292,12 @@ fused_attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
                                                      : umma_idesc(kAccF32, kFmtE4M3, kFmtE4M3, kQTile, D);
       const uint64_t vdesc0 = umma_smem_desc(smem_base + C::OFF_V, kKeyTile);
       for (int j = 0; j < n_tiles; ++j) {
-        PK_TRACE_AT(5, j, 0);
+        PK_STAMP(4, j, 0);
         if (!mbar_wait_bounded(bars.p_ready(j % NP), (j / NP) & 1, abort_flag, W_PV_P)) break;
         if (!mbar_wait_bounded(bars.o_empty(j % NO), (j / NO) & 1, abort_flag, W_PV_O)) break;
         if (!mbar_wait_bounded(bars.v_full(j % NV), (j / NV) & 1, abort_flag, W_PV_V)) break;
         tc_fence_after();
-        PK_TRACE_AT(5, j, 1);
+        PK_STAMP(4, j, 1);
         const uint64_t vdesc = vdesc0 + static_cast<uint64_t>(((j % NV) * C::V_BYTES) >> 4);
         const uint32_t d = tmem_base + C::COL_O + (j % NO) * D;
         const uint32_t a = tmem_base + C::COL_P + (j % NP) * (kKeyTile / 4);
@@ -297,12 +307,12 @@ fused_attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
           else umma_f8_ts(d, a + 8 * kk, vdesc + 2 * kk, idesc_pv, kk > 0);
         }
         tc_commit(bars.pv_done(j % NP));
-        PK_TRACE_AT(5, j, 2);
+        PK_STAMP(4, j, 2);
       }
     }
   } else if (wg < NSWG) {
     // ------------------------------------------------------------------ softmax
-    if (NSWG == 2) setmaxnreg_dec<112>(); else setmaxnreg_dec<128>();
+    if (ALGO == kPiper) { if (PK_REG_SM <= C::LAUNCH_REGS) setmaxnreg_dec<PK_REG_SM>(); else setmaxnreg_inc<PK_REG_SM>(); } else setmaxnreg_dec<128>();
     const int row = tid & 127;
     const uint32_t lane_addr = tmem_base + (static_cast<uint32_t>((warp & 3) * 32) << 16);
     const float qm = prm.q_mul[static_cast<long long>(bh) * prm.sq_pad + q0 + row];
@@ -318,12 +328,12 @@ fused_attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
     // that three different roles share; the chunk after the current one is always in flight.
     const float2 neg_magic2 = make_float2(-kMagic, -kMagic);
     for (int j = wg; j < n_tiles; j += NSWG) {
-      if ((warp & 3) == 0) PK_TRACE_AT(wg, j, 0);
+      PK_STAMP(wg, j, 0);
       // votes keep the warp converged for the .sync.aligned tensor-memory ops even when a wait is abandoned
       if (!__all_sync(0xffffffffu, mbar_wait_bounded(bars.vec_full(j % NVEC), (j / NVEC) & 1, abort_flag, W_SM_VEC))) break;
       if (!__all_sync(0xffffffffu, mbar_wait_bounded(bars.qk_done(j % NK), (j / NK) & 1, abort_flag, W_SM_S))) break;
       tc_fence_after();
-      if ((warp & 3) == 0) PK_TRACE_AT(wg, j, 1);
+      PK_STAMP(wg, j, 1);
       const uint32_t s_addr = lane_addr + C::COL_S + (j % NS) * kKeyTile;
       // Per-key vectors of this tile in shared memory: [0,64) K scale, [64,128) additive term
       // (log2 of the V row scale / 0, -inf on padding), [128,192) 1 / V row scale.
@@ -366,6 +376,85 @@ fused_attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
         }
       };
 
+#if PK_SOFTMAX_UNROLLED
+      // Single pass over registers: the whole 64-column tile is loaded once, the score buffer is
+      // re-armed and returned immediately, and t stays in registers between max and exp.
+      uint32_t sraw[kKeyTile];
+      tmem_ld32(s_addr, sraw);
+      tmem_ld32(s_addr + 32, sraw + 32);
+      tmem_wait_ld();
+      PK_STAMP(wg, j, 4);
+      tmem_arm(s_addr, kKeyTile);
+      float2 t2[kKeyTile / 2];
+#pragma unroll
+      for (int ch = 0; ch < kKeyTile / 16; ++ch) scores16(sraw + ch * 16, ch, t2 + ch * 8);
+      float bm0 = fmaxf(t2[0].x, t2[0].y), bm1 = fmaxf(t2[1].x, t2[1].y);
+#pragma unroll
+      for (int c2 = 2; c2 < kKeyTile / 2; c2 += 2) { bm0 = max3(bm0, t2[c2].x, t2[c2].y); bm1 = max3(bm1, t2[c2 + 1].x, t2[c2 + 1].y); }
+      const float bm = fmaxf(bm0, bm1);
+      tmem_wait_st();
+      tc_fence_before();
+      mbar_arrive(bars.s_free(j % NS));
+      PK_STAMP(wg, j, 2);
+      float shift, ow = 1.f;
+      if (ALGO == kPiper) {
+        shift = (bm == -INFINITY) ? 0.f : -bm;
+      } else {
+        const float nm = fmaxf(m_run, bm);
+        const float ns = (nm == -INFINITY) ? 0.f : nm;
+        ow = (m_run == nm) ? 1.f : ex2_approx(m_run - ns);
+        shift = 8.807354922057604f - ns;  // log2(448): P = e4m3(448 * 2^(t - max))
+        m_run = nm;
+      }
+      const float2 shift2 = make_float2(shift, shift);
+      const float2 c255 = make_float2(255.f, 255.f), magic2 = make_float2(kMagic, kMagic);
+      float2 psum_a = make_float2(0.f, 0.f), psum_b = make_float2(0.f, 0.f);
+      uint32_t packed[kKeyTile / 4];
+#pragma unroll
+      for (int c4 = 0; c4 < kKeyTile / 4; ++c4) {
+        const float2 d0 = __fadd2_rn(t2[c4 * 2 + 0], shift2), d1 = __fadd2_rn(t2[c4 * 2 + 1], shift2);
+        const float2 e0 = make_float2(ex2_approx(d0.x), ex2_approx(d0.y));
+        const float2 e1 = make_float2(ex2_approx(d1.x), ex2_approx(d1.y));
+        if (ALGO == kPiper) {
+          const float4 inv = vk[2 * (kKeyTile / 4) + c4];
+          psum_a = __ffma2_rn(e0, make_float2(inv.x, inv.y), psum_a);
+          psum_b = __ffma2_rn(e1, make_float2(inv.z, inv.w), psum_b);
+          const float2 b0 = __ffma2_rn(e0, c255, magic2), b1 = __ffma2_rn(e1, c255, magic2);  // low byte = rne(255 e)
+          const uint32_t lo = __byte_perm(__float_as_uint(b0.x), __float_as_uint(b0.y), 0x0040);
+          const uint32_t hi = __byte_perm(__float_as_uint(b1.x), __float_as_uint(b1.y), 0x0040);
+          packed[c4] = __byte_perm(lo, hi, 0x5410);
+        } else {
+          psum_a = __fadd2_rn(psum_a, e0);
+          psum_b = __fadd2_rn(psum_b, e1);
+          const uint32_t lo = __nv_cvt_float2_to_fp8x2(e0, __NV_SATFINITE, __NV_E4M3);
+          const uint32_t hi = __nv_cvt_float2_to_fp8x2(e1, __NV_SATFINITE, __NV_E4M3);
+          packed[c4] = __byte_perm(lo, hi, 0x5410);
+        }
+      }
+      PK_STAMP(wg, j, 5);
+      // probability buffer j%NP was last read by the PV product of tile j-NP
+      if (j >= NP && !__all_sync(0xffffffffu, mbar_wait_bounded(bars.pv_done(j % NP), ((j / NP) - 1) & 1, abort_flag, W_SM_PV))) break;
+      tc_fence_after();
+      PK_STAMP(wg, j, 6);
+      const uint32_t p_addr = lane_addr + C::COL_P + (j % NP) * (kKeyTile / 4);
+      tmem_st16(p_addr, packed);
+      if (DUMP) {
+        if (dumping && j == 0) {
+          uint32_t* dp = reinterpret_cast<uint32_t*>(static_cast<char*>(prm.dump) + kQTile * kKeyTile * 4);
+#pragma unroll
+          for (int c = 0; c < kKeyTile / 4; ++c) dp[row * (kKeyTile / 4) + c] = packed[c];
+        }
+      }
+      const float psum = (psum_a.x + psum_a.y) + (psum_b.x + psum_b.y);
+      const float2 st = (ALGO == kPiper) ? make_float2(bm, psum) : make_float2(ow, psum * (1.f / 448.f));
+      stat_ring[(j % NSTAT) * kQTile + row] = st;
+      tmem_wait_st();
+      PK_STAMP(wg, j, 7);
+      tc_fence_before();
+      mbar_arrive(bars.p_ready(j % NP));
+      mbar_arrive(bars.stat_full(j % NSTAT));
+      PK_STAMP(wg, j, 3);
+#else
       // ---- pass 1: tile maximum
       uint32_t sbuf[2][16];
       float bm0 = -INFINITY, bm1 = -INFINITY;
@@ -389,7 +478,7 @@ fused_attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
       tmem_wait_st();
       tmem_ld16(s_addr, sbuf[0]);  // first chunk of pass 2
       const float bm = fmaxf(bm0, bm1);
-      if ((warp & 3) == 0) PK_TRACE_AT(wg, j, 2);
+      PK_STAMP(wg, j, 2);
 
       // probability buffer j%NP was last read by the PV product of tile j-NP
       if (j >= NP && !__all_sync(0xffffffffu, mbar_wait_bounded(bars.pv_done(j % NP), ((j / NP) - 1) & 1, abort_flag, W_SM_PV))) break;
@@ -462,31 +551,34 @@ fused_attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
       mbar_arrive(bars.s_free(j % NS));
       mbar_arrive(bars.p_ready(j % NP));
       mbar_arrive(bars.stat_full(j % NSTAT));
-      if ((warp & 3) == 0) PK_TRACE_AT(wg, j, 3);
+      PK_STAMP(wg, j, 3);
+#endif
     }
-  } else if (wg == NSWG) {
+  } else if (wg < NSWG + C::NDQ) {
     // ------------------------------------------------------------------ dequant + epilogue
-    if (NSWG == 2) setmaxnreg_inc<232>(); else setmaxnreg_inc<232>();
+    if (ALGO == kPiper) setmaxnreg_inc<PK_REG_DQ>(); else setmaxnreg_inc<(C::NDQ == 1 ? 232 : 136)>();
+    constexpr int DH = D / C::NDQ;          // columns folded by this warpgroup
+    const int col0 = (wg - NSWG) * DH;      // first of them
     const int row = tid & 127;
     const uint32_t lane_addr = tmem_base + (static_cast<uint32_t>((warp & 3) * 32) << 16);
     if (O_MAGIC) {
-      tmem_arm(lane_addr + C::COL_O, NO * D);
+      for (int i = 0; i < NO; ++i) tmem_arm(lane_addr + C::COL_O + i * D + col0, DH);
       tmem_wait_st();
     }
     tc_fence_before();
     for (int i = 0; i < NO; ++i) mbar_arrive(bars.o_empty(i));
 
-    float2 num2[D / 2];
+    float2 num2[DH / 2];
 #pragma unroll
-    for (int d = 0; d < D / 2; ++d) num2[d] = make_float2(0.f, 0.f);
+    for (int d = 0; d < DH / 2; ++d) num2[d] = make_float2(0.f, 0.f);
     float den = 0.f, m = -INFINITY;
     bool ok = true;
-    for (int j = 0; j < n_tiles; ++j) {
-      if ((warp & 3) == 0) PK_TRACE_AT(2, j, 0);
-      if (!__all_sync(0xffffffffu, mbar_wait_bounded(bars.stat_full(j % NSTAT), (j / NSTAT) & 1, abort_flag, W_DQ_STAT))) { ok = false; break; }
+    // Row statistics recurrence (running max, denominator, rescale factors); it depends only
+    // on the published per-tile statistics, so it is evaluated one tile ahead of the fold.
+    float ow = 1.f, c = 0.f;
+    auto advance_stats = [&](int j) -> bool {
+      if (!__all_sync(0xffffffffu, mbar_wait_bounded(bars.stat_full(j % NSTAT), (j / NSTAT) & 1, abort_flag, W_DQ_STAT))) return false;
       const float2 st = stat_ring[(j % NSTAT) * kQTile + row];
-      if ((warp & 3) == 0) PK_TRACE_AT(2, j, 1);
-      float ow, c;
       if (ALGO == kPiper) {
         const float bm = st.x;
         const float nm = fmaxf(m, bm);
@@ -497,45 +589,60 @@ fused_attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
           cw = (bm == nm) ? 1.f : ex2_approx(bm - nm);
         }
         den = fmaf(den, ow, st.y * cw);
-        c = __fdiv_rn(cw, 255.f);
+        c = cw * (1.f / 255.f);
         m = nm;
       } else {
         ow = st.x;
         den = fmaf(den, ow, st.y);
         c = 1.f;
       }
-      if (!__all_sync(0xffffffffu, mbar_wait_bounded(bars.pv_done(j % NP), (j / NP) & 1, abort_flag, W_DQ_O))) { ok = false; break; }
-      tc_fence_after();
-      if ((warp & 3) == 0) PK_TRACE_AT(2, j, 2);
-      const uint32_t o_addr = lane_addr + C::COL_O + (j % NO) * D;
-      // The partial is read 16 columns at a time; the next chunk's load is in flight while the
-      // current one is folded into the numerator, and each chunk is re-armed as soon as read.
-      uint32_t obuf[2][16];
-      tmem_ld16(o_addr, obuf[0]);
+      return true;
+    };
+    // The partial is read 16 columns at a time; the next chunk's load is always in flight while
+    // the current one is folded, across tile boundaries too: the first chunk of tile j+1 is
+    // requested before the last chunk of tile j is folded.  Each chunk is re-armed once read.
+    uint32_t obuf[2][16];
+    const float2 neg_magic2 = make_float2(-kMagic, -kMagic);
+    if (n_tiles > 0) {
+      ok = advance_stats(0);
+      ok = ok && __all_sync(0xffffffffu, mbar_wait_bounded(bars.pv_done(0), 0, abort_flag, W_DQ_O));
+      if (ok) {
+        tc_fence_after();
+        tmem_ld16(lane_addr + C::COL_O + col0, obuf[0]);
+      }
+    }
+    for (int j = 0; ok && j < n_tiles; ++j) {
+      PK_STAMP(2, j, 0);
+      const uint32_t o_addr = lane_addr + C::COL_O + (j % NO) * D + col0;
       if (__any_sync(0xffffffffu, ow != 1.f)) {
         const float2 ow2 = make_float2(ow, ow);
 #pragma unroll
-        for (int d = 0; d < D / 2; ++d) num2[d] = __fmul2_rn(num2[d], ow2);
+        for (int d = 0; d < DH / 2; ++d) num2[d] = __fmul2_rn(num2[d], ow2);
       }
       const float2 c2 = make_float2(c, c);
-      const float2 neg_magic2 = make_float2(-kMagic, -kMagic);
-      if ((warp & 3) == 0) PK_TRACE_AT(4, j, 0);
+      PK_STAMP(2, j, 1);
 #pragma unroll
-      for (int ch = 0; ch < D / 16; ++ch) {
+      for (int ch = 0; ch < DH / 16; ++ch) {
         tmem_wait_ld();
-        if ((warp & 3) == 0 && ch == 0) PK_TRACE_AT(4, j, 1);
-        if ((warp & 3) == 0 && ch == 1) PK_TRACE_AT(4, j, 2);
-        if (ch + 1 < D / 16) tmem_ld16(o_addr + (ch + 1) * 16, obuf[(ch + 1) & 1]);
+        if (ch == 0) PK_STAMP(2, j, 2);
+        if (ch + 1 < DH / 16) {
+          tmem_ld16(o_addr + (ch + 1) * 16, obuf[(ch + 1) & 1]);
+        } else if (j + 1 < n_tiles) {
+          // statistics and first chunk of the next tile (its product does not depend on this fold)
+          ok = advance_stats(j + 1);
+          ok = ok && __all_sync(0xffffffffu, mbar_wait_bounded(bars.pv_done((j + 1) % NP), ((j + 1) / NP) & 1, abort_flag, W_DQ_O));
+          if (ok) {
+            tc_fence_after();
+            tmem_ld16(lane_addr + C::COL_O + ((j + 1) % NO) * D + col0, obuf[(ch + 1) & 1]);
+          }
+        }
         if (O_MAGIC) tmem_arm(o_addr + ch * 16, 16);
         const uint32_t* o = obuf[ch & 1];
         if (DUMP && dumping && j == 0) {
           uint32_t* dp = reinterpret_cast<uint32_t*>(static_cast<char*>(prm.dump) + kQTile * kKeyTile * 5);
 #pragma unroll
-          for (int i = 0; i < 16; ++i) dp[row * D + ch * 16 + i] = O_MAGIC ? o[i] - kMagicBits : o[i];
+          for (int i = 0; i < 16; ++i) dp[row * D + col0 + ch * 16 + i] = O_MAGIC ? o[i] - kMagicBits : o[i];
         }
-#ifdef PK_TRACE
-        if (prm.ablate & 2) { num2[ch].x += __uint_as_float(o[0] ^ o[15]); continue; }
-#endif
 #pragma unroll
         for (int i = 0; i < 8; ++i) {
           float2 y = make_float2(__uint_as_float(o[2 * i]), __uint_as_float(o[2 * i + 1]));
@@ -548,11 +655,11 @@ fused_attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
           }
         }
       }
-      if ((warp & 3) == 0) PK_TRACE_AT(4, j, 3);
+      PK_STAMP(2, j, 6);
       if (O_MAGIC) tmem_wait_st();
       tc_fence_before();
       mbar_arrive(bars.o_empty(j % NO));
-      if ((warp & 3) == 0) PK_TRACE_AT(2, j, 3);
+      PK_STAMP(2, j, 3);
     }
     // epilogue: normalise, restore the V mean (piper) / apply the channel scale (sage), cast
     const int grow = q0 + row;
@@ -560,10 +667,10 @@ fused_attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
       // one IEEE division per row; the D per-element divisions of the reference become
       // multiplications by the reciprocal (at most an ulp apart, and far less code)
       const float dinv = __fdiv_rn(1.f, fmaxf(den, 1e-30f));
-      const float* aux = prm.v_aux + static_cast<long long>(bh) * D;
-      const long long obase = (static_cast<long long>(bh) * prm.Sq + grow) * D;
+      const float* aux = prm.v_aux + static_cast<long long>(bh) * D + col0;
+      const long long obase = (static_cast<long long>(bh) * prm.Sq + grow) * D + col0;
 #pragma unroll
-      for (int d0 = 0; d0 < D; d0 += 8) {
+      for (int d0 = 0; d0 < DH; d0 += 8) {
         float r[8];
 #pragma unroll
         for (int i = 0; i < 8; ++i) {
@@ -637,7 +744,7 @@ int make_map(CUtensorMap* m, void* base, uint64_t rows, uint64_t cols, uint32_t 
   return PK_OK;
 }
 
-template <int D, int ALGO, bool KPB, bool DUMP>
+template <int D, int ALGO, bool KPB, int DEBUG>
 int launch_one_impl(const pk_problem& p, const Layout& L, cudaStream_t st, const DebugDump* dump) {
   using C = Cfg<D, ALGO>;
   CUtensorMap tq, tk, tv;
@@ -659,11 +766,9 @@ int launch_one_impl(const pk_problem& p, const Layout& L, cudaStream_t st, const
   prm.dump = dump ? dump->ptr : nullptr;
   prm.dump_bh = dump ? dump->bh : -1;
   prm.dump_qt = dump ? dump->q_tile : -1;
-  prm.ablate = 0;
-#ifdef PK_TRACE
-  if (const char* a = getenv("PK_ABLATE")) prm.ablate = atoi(a);
-#endif
-  auto kern = fused_attention_kernel<D, ALGO, KPB, DUMP>;
+  prm.timeline = dump ? static_cast<long long*>(dump->timeline) : nullptr;
+  prm.timeline_tiles = dump ? dump->timeline_tiles : 0;
+  auto kern = fused_attention_kernel<D, ALGO, KPB, DEBUG>;
   {
     const cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES);
     if (e != cudaSuccess) return fail(PK_ERR_CUDA, "cudaFuncSetAttribute: %s", cuda_err(e));
@@ -677,7 +782,9 @@ int launch_one_impl(const pk_problem& p, const Layout& L, cudaStream_t st, const
 
 template <int D, int ALGO, bool KPB>
 int launch_one(const pk_problem& p, const Layout& L, cudaStream_t st, const DebugDump* dump) {
-  return dump ? launch_one_impl<D, ALGO, KPB, true>(p, L, st, dump) : launch_one_impl<D, ALGO, KPB, false>(p, L, st, dump);
+  if (dump && dump->ptr) return launch_one_impl<D, ALGO, KPB, 1>(p, L, st, dump);
+  if (dump && dump->timeline) return launch_one_impl<D, ALGO, KPB, 2>(p, L, st, dump);
+  return launch_one_impl<D, ALGO, KPB, 0>(p, L, st, dump);
 }
 
 template <int D, int ALGO>

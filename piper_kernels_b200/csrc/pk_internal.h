@@ -42,8 +42,10 @@ int kv_means_static(const pk_problem& p, float* k_mean, float* v_mean);
 
 // Fused kernels (fused_attention.cu).
 struct DebugDump {
-  void* ptr;
-  int bh, q_tile;
+  void* ptr;        // first-tile intermediates (may be null)
+  int bh, q_tile;   // which CTA
+  void* timeline;   // per-role clock stamps (may be null)
+  int timeline_tiles;
 };
 int launch_fused(const pk_problem& p, const Layout& L, Algo algo, cudaStream_t stream,
                  const DebugDump* dump);

@@ -1,0 +1,86 @@
+"""Per-role timeline of one CTA of the fused kernel (profiling aid).
+
+    python -m piper_kernels_b200.timeline [--workload c2] [--bh 5] [--q-tile 7]
+
+Runs the ordinary fused kernel through ``pk_debug_timeline`` and prints, per warp role, the
+average cycles per key tile spent waiting and working, plus the steady-state tile period.
+"""
+
+from __future__ import annotations
+
+import argparse
+import ctypes as C
+
+import numpy as np
+import torch
+
+from . import _cabi
+from .attention.piper import default_center_value, should_sort_value_rows
+from .runtime import AttentionCall
+from .workloads import WORKLOADS, make_inputs
+
+ROLES = 6
+
+
+def capture(call: AttentionCall, bh: int, q_tile: int, max_tiles: int = 1024) -> np.ndarray:
+    buf = torch.zeros(ROLES * max_tiles * 8, dtype=torch.int64, device=call.q.device)
+    call._sync_stream()
+    _cabi.check(call.lib.pk_debug_timeline(C.byref(call.p), int(call.algo != "piper"), bh, q_tile, buf.data_ptr(), max_tiles))
+    torch.cuda.synchronize(call.q.device)
+    return buf.cpu().numpy().reshape(ROLES, max_tiles, 8)
+
+
+def summarize(tr: np.ndarray, n_tiles: int, nswg: int) -> str:
+    n = min(n_tiles, tr.shape[1])
+    t0 = tr[tr > 0].min()
+    tr = np.where(tr > 0, tr - t0, -1)[:, :n]
+    lo, hi = min(8, n // 4), n - 2
+    lines = [f"tiles {n}; total {int(tr.max())} cycles; steady-state period {(tr[2, hi, 3] - tr[2, lo, 3]) / (hi - lo):.0f} cycles per tile"]
+    for w in range(nswg):
+        x = tr[w, lo + ((w - lo) % nswg):hi:nswg]
+        lines.append(f"softmax{w}: wait {np.mean(x[:, 1] - x[:, 0]):.0f}  pass1 {np.mean(x[:, 2] - x[:, 1]):.0f}  "
+                     f"pass2+publish {np.mean(x[:, 3] - x[:, 2]):.0f}  per own tile {np.mean(np.diff(x[:, 0])):.0f}")
+    x = tr[2, lo:hi]
+    lines.append(f"dequant : wait stats {np.mean(x[:, 1] - x[:, 0]):.0f}  wait PV {np.mean(x[:, 2] - x[:, 1]):.0f}  "
+                 f"fold {np.mean(x[:, 3] - x[:, 2]):.0f}  per tile {np.mean(np.diff(x[:, 0])):.0f}")
+    for r, name in ((3, "S issue "), (4, "PV issue")):
+        x = tr[r, lo:hi]
+        lines.append(f"{name}: wait {np.mean(x[:, 1] - x[:, 0]):.0f}  issue {np.mean(x[:, 2] - x[:, 1]):.0f}  per tile {np.mean(np.diff(x[:, 0])):.0f}")
+    own = np.arange(n) % nswg
+    p_done = tr[own, np.arange(n), 3]
+    lines.append(f"P published -> PV issued: {np.mean(tr[4, lo:hi, 2] - p_done[lo:hi]):.0f}; "
+                 f"PV issued -> dequant starts folding: {np.mean(tr[2, lo:hi, 2] - tr[4, lo:hi, 2]):.0f}; "
+                 f"S issued -> softmax picks it up: {np.mean(tr[own, np.arange(n), 1][lo:hi] - tr[3, lo:hi, 2]):.0f}")
+    return "\n".join(lines)
+
+
+def main() -> None:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--workload", default="c2")
+    ap.add_argument("--bh", type=int, default=5)
+    ap.add_argument("--q-tile", type=int, default=7)
+    ap.add_argument("--save", default=None, help="write the raw stamps to this .npy file")
+    a = ap.parse_args()
+    w = WORKLOADS[a.workload]
+    dev = torch.device("cuda:0")
+    q, k, v = make_inputs(w, dev)
+    scale = w.head_dim ** -0.5
+    if w.op == "piper":
+        center = default_center_value(q, k, w.causal) if w.center is None else bool(w.center)
+        sort = should_sort_value_rows(center_value=center, is_causal=w.causal, head_dim=w.head_dim, key_length=w.kv_len)
+        call = AttentionCall("piper", q, k, v, scale, w.causal, center=center, sort=sort)
+    else:
+        call = AttentionCall("sage2pp", q, k, v, scale, w.causal)
+    call.prepare().run()
+    torch.cuda.synchronize()
+    tr = capture(call, a.bh, a.q_tile)
+    n_tiles = (w.kv_len + 63) // 64
+    if w.causal:
+        n_tiles = min(n_tiles, 2 * a.q_tile + 2)
+    print(summarize(tr, n_tiles, 2 if w.op == "piper" else 1))
+    if a.save:
+        np.save(a.save, tr)
+
+
+if __name__ == "__main__":
+    main()
