@@ -40,6 +40,9 @@
 #ifndef PK_SOFTMAX_UNROLLED
 #define PK_SOFTMAX_UNROLLED 1
 #endif
+#ifndef PK_S_VARIANT
+#define PK_S_VARIANT 0
+#endif
 #ifndef PK_NDQ
 #define PK_NDQ 1
 #endif
@@ -280,7 +283,7 @@ fused_attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
         const uint64_t kdesc = kdesc0 + static_cast<uint64_t>(((j % NK) * C::K_BYTES) >> 4);
         const uint32_t d = tmem_base + C::COL_S + (j % NS) * kKeyTile;
 #pragma unroll
-        for (int kk = 0; kk < D / 32; ++kk) umma_i8_ss(d, qdesc + 2 * kk, kdesc + 2 * kk, idesc_qk, 1u);
+        for (int kk = 0; kk < D / 32; ++kk) umma_i8_ss(d, qdesc + 2 * kk, kdesc + 2 * kk, idesc_qk, (PK_S_VARIANT == 2 && kk == 0) ? 0u : 1u);
         tc_commit(bars.qk_done(j % NK));
         PK_STAMP(3, j, 2);
       }
@@ -384,7 +387,15 @@ fused_attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
       tmem_ld32(s_addr + 32, sraw + 32);
       tmem_wait_ld();
       PK_STAMP(wg, j, 4);
+#if PK_S_VARIANT == 2
+      // no re-arming: the score buffer is free as soon as it has been read
+      tc_fence_before();
+      mbar_arrive(bars.s_free(j % NS));
+#pragma unroll
+      for (int c = 0; c < kKeyTile; ++c) sraw[c] += kMagicBits;
+#else
       tmem_arm(s_addr, kKeyTile);
+#endif
       float2 t2[kKeyTile / 2];
 #pragma unroll
       for (int ch = 0; ch < kKeyTile / 16; ++ch) scores16(sraw + ch * 16, ch, t2 + ch * 8);
@@ -392,9 +403,11 @@ fused_attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
 #pragma unroll
       for (int c2 = 2; c2 < kKeyTile / 2; c2 += 2) { bm0 = max3(bm0, t2[c2].x, t2[c2].y); bm1 = max3(bm1, t2[c2 + 1].x, t2[c2 + 1].y); }
       const float bm = fmaxf(bm0, bm1);
+#if PK_S_VARIANT == 0
       tmem_wait_st();
       tc_fence_before();
       mbar_arrive(bars.s_free(j % NS));
+#endif
       PK_STAMP(wg, j, 2);
       float shift, ow = 1.f;
       if (ALGO == kPiper) {
@@ -451,6 +464,9 @@ fused_attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
       tmem_wait_st();
       PK_STAMP(wg, j, 7);
       tc_fence_before();
+#if PK_S_VARIANT == 1
+      mbar_arrive(bars.s_free(j % NS));
+#endif
       mbar_arrive(bars.p_ready(j % NP));
       mbar_arrive(bars.stat_full(j % NSTAT));
       PK_STAMP(wg, j, 3);
