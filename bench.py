@@ -32,6 +32,11 @@ sys.path.insert(0, str(ROOT))
 METRIC = "attention_tops"
 UNIT = "TOPS"
 NOMINAL_INT8_TOPS = 4500.0
+# DRAM bytes per launch of the fused kernel per query row (read + write), from the ncu capture of
+# workload c2 summarised in profiles/fused_attention_kernel_c2_ncu_full.md: 98.4 MB for 48 heads
+# x 4096 rows at D=128.  Traffic grows with batch*heads*rows (K/V of a head stay in L2 while its
+# query tiles run), so other D=128 workloads scale by their row count.
+FUSED_DRAM_BYTES_PER_ROW_D128 = 98.4e6 / (48 * 4096)
 
 
 def parse_args():
@@ -114,18 +119,20 @@ def reference_arm(args, w, rank, world):
         return
     threads = os.cpu_count() or 1
     per_step = max(2.0, min(20.0, 120.0 / max(1, args.steps + args.warmup)))
-    vals = []
+    vals, times = [], []
     desc = ""
     for i in range(args.warmup + args.steps):
+        t0 = time.perf_counter()
         tops, desc = cpu_reference_tops(w, per_step, threads)
         if i >= args.warmup:
             vals.append(tops)
+            times.append((time.perf_counter() - t0) * 1e3)
     value = statistics.mean(vals)
     rows_ops = None
     line = {
         "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
-        "warmup": args.warmup, "ms_per_step": None, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
-        "dtype": "int8", "data": "synthetic", "config": workload_config(w, args.gpus),
+        "warmup": args.warmup, "ms_per_step": statistics.mean(times), "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "int8", "data": "synthetic", "config": workload_config(w, args.gpus),
         "cpu_baseline": {"value": value, "unit": UNIT, "cores": threads, "kind": "port", "sample": desc},
         "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
@@ -255,29 +262,33 @@ def ours_arm(args, w, rank, local_rank, world):
     status = call.status()
     del call
 
-    # end to end from pinned host memory
+    # end to end from pinned host memory through the public host entry point: per-head-chunk upload,
+    # compute and download overlap on three streams (heads are independent)
     e2e = None
     if not args.no_e2e:
-        hq, hk, hv = (t.contiguous().cpu().pin_memory() for t in (q, k, v))
+        from piper_kernels_b200.scheduler import attention_from_host
+
+        hq = q.contiguous().cpu().pin_memory()
+        if w.name == "c5":  # keep the interleaved K/V layout (sequence stride 2*D) in host memory too
+            kv_host = torch.stack((k, v), dim=3).contiguous().cpu().pin_memory()
+            hk, hv = kv_host[:, :, :, 0, :], kv_host[:, :, :, 1, :]
+        else:
+            hk, hv = k.contiguous().cpu().pin_memory(), v.contiguous().cpu().pin_memory()
         hout = torch.empty(q.shape, dtype=q.dtype).pin_memory()
-        if w.name == "c5":  # keep the interleaved K/V layout on the device side
-            kv_host = torch.stack((hk, hv), dim=3).contiguous().pin_memory()
+        kwargs = dict(is_causal=w.causal, center_value=w.center) if w.op == "piper" else dict(is_causal=w.causal)
+        fn = pk.piper_attention if w.op == "piper" else pk.sage_attention_2pp
+        chunk = max(1, min(8, w.flat_heads // 4))
 
         def e2e_step():
-            dq = hq.to(dev, non_blocking=True)
-            if w.name == "c5":
-                dkv = kv_host.to(dev, non_blocking=True)
-                dk, dv = dkv[:, :, :, 0, :], dkv[:, :, :, 1, :]
-            else:
-                dk, dv = hk.to(dev, non_blocking=True), hv.to(dev, non_blocking=True)
-            hout.copy_(op(dq, dk, dv), non_blocking=True)
+            attention_from_host(fn, hq, hk, hv, hout, dev, heads_per_chunk=chunk, **kwargs)
 
         for _ in range(2):
             e2e_step()
         e2e_ms = max_over_ranks(timed(e2e_step, args.steps, sync, barrier))
         h2d = sum(t.numel() * t.element_size() for t in (hq, hk, hv))
         e2e = {"value": world * ops_per_gpu / (e2e_ms * 1e-3) / 1e12, "unit": UNIT, "ms_per_step": e2e_ms,
-               "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": hout.numel() * hout.element_size()}
+               "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": hout.numel() * hout.element_size(),
+               "api": f"scheduler.attention_from_host, {chunk} heads per chunk, pinned host buffers"}
 
     if rank != 0:
         if dist is not None:
@@ -295,7 +306,10 @@ def ours_arm(args, w, rank, local_rank, world):
     achieved = ops_per_gpu / (fused_ms * 1e-3) / 1e12
     roofline = {
         "bound": "tensor", "kernel": "fused_attention_kernel", "achieved": achieved, "peak": peak, "unit": "TFLOP/s",
-        "frac": achieved / peak, "traffic": None, "peak_note": peak_note,
+        "frac": achieved / peak,
+        "traffic": (FUSED_DRAM_BYTES_PER_ROW_D128 * w.flat_heads * w.q_len if (w.head_dim == 128 and w.q_len == w.kv_len) else None),
+        "traffic_note": "bytes per launch, scaled from the ncu capture of c2 by rows processed",
+        "peak_note": peak_note,
         "frac_of_nominal_int8": achieved / NOMINAL_INT8_TOPS, "ms_per_launch": fused_ms, "prepass_ms": prep_ms,
     }
     cpu_baseline = None

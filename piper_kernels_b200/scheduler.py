@@ -49,3 +49,46 @@ def gather_outputs(local: torch.Tensor, mine: range, flat_heads: int, shape, gro
         if stop > start:
             full[start:stop] = piece[0]
     return full.reshape(shape)
+
+
+def attention_from_host(op, q_host: torch.Tensor, k_host: torch.Tensor, v_host: torch.Tensor,
+                        out_host: torch.Tensor, device, *, heads_per_chunk: int = 8, **kwargs) -> torch.Tensor:
+    """Run ``op`` on inputs that live in (pinned) host memory and write the result to host memory.
+
+    Heads are independent, so the flat (batch x heads) axis is cut into chunks; the upload of
+    chunk i+1, the compute of chunk i and the download of chunk i-1 overlap on three CUDA
+    streams.  ``q_host``/``k_host``/``v_host`` are ``[B,H,S,D]`` (``k_host``/``v_host`` may be
+    strided views of one buffer); ``out_host`` is a contiguous ``[B,H,Sq,D]`` host tensor.
+    Returns ``out_host`` after synchronising the three streams.
+    """
+    device = torch.device(device)
+    b, h = q_host.shape[:2]
+    flat = b * h
+    fq, fk, fv = (t.flatten(0, 1) for t in (q_host, k_host, v_host))
+    fo = out_host.view(flat, *out_host.shape[2:])
+    up, down = torch.cuda.Stream(device), torch.cuda.Stream(device)
+    main = torch.cuda.current_stream(device)
+    up.wait_stream(main)
+    down.wait_stream(main)
+    pending = None
+    for start in range(0, flat, heads_per_chunk):
+        sl = slice(start, min(flat, start + heads_per_chunk))
+        with torch.cuda.stream(up):
+            dq, dk, dv = (t[sl].to(device, non_blocking=True).unsqueeze(0) for t in (fq, fk, fv))
+            uploaded = torch.cuda.Event()
+            uploaded.record(up)
+        main.wait_event(uploaded)
+        for t in (dq, dk, dv):
+            t.record_stream(main)
+        out = op(dq, dk, dv, **kwargs)
+        computed = torch.cuda.Event()
+        computed.record(main)
+        with torch.cuda.stream(down):
+            down.wait_event(computed)
+            out.record_stream(down)
+            fo[sl].copy_(out[0], non_blocking=True)
+        pending = (dq, dk, dv, out)
+    del pending
+    main.wait_stream(down)
+    main.wait_stream(up)
+    return out_host
