@@ -266,7 +266,7 @@ def ours_arm(args, w, rank, local_rank, world):
     # compute and download overlap on three streams (heads are independent)
     e2e = None
     if not args.no_e2e:
-        from piper_kernels_b200.scheduler import attention_from_host
+        from piper_kernels_b200.scheduler import HostAttentionPipeline
 
         hq = q.contiguous().cpu().pin_memory()
         if w.name == "c5":  # keep the interleaved K/V layout (sequence stride 2*D) in host memory too
@@ -278,9 +278,10 @@ def ours_arm(args, w, rank, local_rank, world):
         kwargs = dict(is_causal=w.causal, center_value=w.center) if w.op == "piper" else dict(is_causal=w.causal)
         fn = pk.piper_attention if w.op == "piper" else pk.sage_attention_2pp
         chunk = max(1, min(8, w.flat_heads // 4))
+        pipe = HostAttentionPipeline(dev, heads_per_chunk=chunk)
 
         def e2e_step():
-            attention_from_host(fn, hq, hk, hv, hout, dev, heads_per_chunk=chunk, **kwargs)
+            pipe(fn, hq, hk, hv, hout, **kwargs)
 
         for _ in range(2):
             e2e_step()
@@ -288,7 +289,7 @@ def ours_arm(args, w, rank, local_rank, world):
         h2d = sum(t.numel() * t.element_size() for t in (hq, hk, hv))
         e2e = {"value": world * ops_per_gpu / (e2e_ms * 1e-3) / 1e12, "unit": UNIT, "ms_per_step": e2e_ms,
                "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": hout.numel() * hout.element_size(),
-               "api": f"scheduler.attention_from_host, {chunk} heads per chunk, pinned host buffers"}
+               "api": f"scheduler.HostAttentionPipeline, {chunk} heads per chunk, pinned host buffers"}
 
     if rank != 0:
         if dist is not None:

@@ -51,44 +51,70 @@ def gather_outputs(local: torch.Tensor, mine: range, flat_heads: int, shape, gro
     return full.reshape(shape)
 
 
-def attention_from_host(op, q_host: torch.Tensor, k_host: torch.Tensor, v_host: torch.Tensor,
-                        out_host: torch.Tensor, device, *, heads_per_chunk: int = 8, **kwargs) -> torch.Tensor:
-    """Run ``op`` on inputs that live in (pinned) host memory and write the result to host memory.
+class HostAttentionPipeline:
+    """Attention on inputs and outputs that live in pinned host memory.
 
     Heads are independent, so the flat (batch x heads) axis is cut into chunks; the upload of
     chunk i+1, the compute of chunk i and the download of chunk i-1 overlap on three CUDA
-    streams.  ``q_host``/``k_host``/``v_host`` are ``[B,H,S,D]`` (``k_host``/``v_host`` may be
-    strided views of one buffer); ``out_host`` is a contiguous ``[B,H,Sq,D]`` host tensor.
-    Returns ``out_host`` after synchronising the three streams.
+    streams.  Device staging buffers (two slots per tensor) are allocated once and re-used.
     """
-    device = torch.device(device)
-    b, h = q_host.shape[:2]
-    flat = b * h
-    fq, fk, fv = (t.flatten(0, 1) for t in (q_host, k_host, v_host))
-    fo = out_host.view(flat, *out_host.shape[2:])
-    up, down = torch.cuda.Stream(device), torch.cuda.Stream(device)
-    main = torch.cuda.current_stream(device)
-    up.wait_stream(main)
-    down.wait_stream(main)
-    pending = None
-    for start in range(0, flat, heads_per_chunk):
-        sl = slice(start, min(flat, start + heads_per_chunk))
-        with torch.cuda.stream(up):
-            dq, dk, dv = (t[sl].to(device, non_blocking=True).unsqueeze(0) for t in (fq, fk, fv))
-            uploaded = torch.cuda.Event()
-            uploaded.record(up)
-        main.wait_event(uploaded)
-        for t in (dq, dk, dv):
-            t.record_stream(main)
-        out = op(dq, dk, dv, **kwargs)
-        computed = torch.cuda.Event()
-        computed.record(main)
-        with torch.cuda.stream(down):
-            down.wait_event(computed)
-            out.record_stream(down)
-            fo[sl].copy_(out[0], non_blocking=True)
-        pending = (dq, dk, dv, out)
-    del pending
-    main.wait_stream(down)
-    main.wait_stream(up)
-    return out_host
+
+    def __init__(self, device, *, heads_per_chunk: int = 8):
+        self.device = torch.device(device)
+        self.heads_per_chunk = int(heads_per_chunk)
+        self.up = torch.cuda.Stream(self.device)
+        self.down = torch.cuda.Stream(self.device)
+        self._slots = None
+        self._key = None
+
+    def _staging(self, q, k, v):
+        key = (tuple(q.shape[2:]), tuple(k.shape[2:]), q.dtype)
+        if self._key != key:
+            n = self.heads_per_chunk
+            mk = lambda t: torch.empty((n, *t.shape[2:]), dtype=t.dtype, device=self.device)  # noqa: E731
+            self._slots = [{"q": mk(q), "k": mk(k), "v": mk(v), "out": mk(q), "free": None, "drained": None} for _ in range(2)]
+            self._key = key
+        return self._slots
+
+    def __call__(self, op, q_host, k_host, v_host, out_host, **kwargs) -> torch.Tensor:
+        b, h = q_host.shape[:2]
+        flat = b * h
+        fq, fk, fv = (t.flatten(0, 1) for t in (q_host, k_host, v_host))
+        fo = out_host.view(flat, *out_host.shape[2:])
+        slots = self._staging(q_host, k_host, v_host)
+        main = torch.cuda.current_stream(self.device)
+        self.up.wait_stream(main)
+        self.down.wait_stream(main)
+        for i, start in enumerate(range(0, flat, self.heads_per_chunk)):
+            n = min(flat, start + self.heads_per_chunk) - start
+            sl = slice(start, start + n)
+            slot = slots[i % 2]
+            with torch.cuda.stream(self.up):
+                if slot["free"] is not None:
+                    self.up.wait_event(slot["free"])  # the compute that read this slot has finished
+                slot["q"][:n].copy_(fq[sl], non_blocking=True)
+                slot["k"][:n].copy_(fk[sl], non_blocking=True)
+                slot["v"][:n].copy_(fv[sl], non_blocking=True)
+                uploaded = torch.cuda.Event()
+                uploaded.record(self.up)
+            main.wait_event(uploaded)
+            if slot["drained"] is not None:
+                main.wait_event(slot["drained"])  # the download of this slot's previous result has finished
+            out = op(slot["q"][:n].unsqueeze(0), slot["k"][:n].unsqueeze(0), slot["v"][:n].unsqueeze(0), **kwargs)
+            slot["out"][:n].copy_(out[0])
+            slot["free"] = torch.cuda.Event()
+            slot["free"].record(main)
+            with torch.cuda.stream(self.down):
+                self.down.wait_event(slot["free"])
+                fo[sl].copy_(slot["out"][:n], non_blocking=True)
+                slot["drained"] = torch.cuda.Event()
+                slot["drained"].record(self.down)
+        main.wait_stream(self.down)
+        main.wait_stream(self.up)
+        return out_host
+
+
+def attention_from_host(op, q_host: torch.Tensor, k_host: torch.Tensor, v_host: torch.Tensor,
+                        out_host: torch.Tensor, device, *, heads_per_chunk: int = 8, **kwargs) -> torch.Tensor:
+    """One-shot form of :class:`HostAttentionPipeline` (allocates the staging buffers per call)."""
+    return HostAttentionPipeline(device, heads_per_chunk=heads_per_chunk)(op, q_host, k_host, v_host, out_host, **kwargs)
