@@ -43,6 +43,9 @@
 #ifndef PK_S_VARIANT
 #define PK_S_VARIANT 0
 #endif
+#ifndef PK_DQ_CHUNK
+#define PK_DQ_CHUNK 16
+#endif
 #ifndef PK_NDQ
 #define PK_NDQ 1
 #endif
@@ -574,6 +577,7 @@ fused_attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
     // ------------------------------------------------------------------ dequant + epilogue
     if (ALGO == kPiper) setmaxnreg_inc<PK_REG_DQ>(); else setmaxnreg_inc<(C::NDQ == 1 ? 232 : 136)>();
     constexpr int DH = D / C::NDQ;          // columns folded by this warpgroup
+    constexpr int CH = (DH % PK_DQ_CHUNK == 0) ? PK_DQ_CHUNK : 16;  // columns per tensor-memory round trip
     const int col0 = (wg - NSWG) * DH;      // first of them
     const int row = tid & 127;
     const uint32_t lane_addr = tmem_base + (static_cast<uint32_t>((warp & 3) * 32) << 16);
@@ -617,14 +621,14 @@ fused_attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
     // The partial is read 16 columns at a time; the next chunk's load is always in flight while
     // the current one is folded, across tile boundaries too: the first chunk of tile j+1 is
     // requested before the last chunk of tile j is folded.  Each chunk is re-armed once read.
-    uint32_t obuf[2][16];
+    uint32_t obuf[2][CH];
     const float2 neg_magic2 = make_float2(-kMagic, -kMagic);
     if (n_tiles > 0) {
       ok = advance_stats(0);
       ok = ok && __all_sync(0xffffffffu, mbar_wait_bounded(bars.pv_done(0), 0, abort_flag, W_DQ_O));
       if (ok) {
         tc_fence_after();
-        tmem_ld16(lane_addr + C::COL_O + col0, obuf[0]);
+        tmem_ldN<CH>(lane_addr + C::COL_O + col0, obuf[0]);
       }
     }
     for (int j = 0; ok && j < n_tiles; ++j) {
@@ -638,36 +642,36 @@ fused_attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
       const float2 c2 = make_float2(c, c);
       PK_STAMP(2, j, 1);
 #pragma unroll
-      for (int ch = 0; ch < DH / 16; ++ch) {
+      for (int ch = 0; ch < DH / CH; ++ch) {
         tmem_wait_ld();
         if (ch == 0) PK_STAMP(2, j, 2);
-        if (ch + 1 < DH / 16) {
-          tmem_ld16(o_addr + (ch + 1) * 16, obuf[(ch + 1) & 1]);
+        if (ch + 1 < DH / CH) {
+          tmem_ldN<CH>(o_addr + (ch + 1) * CH, obuf[(ch + 1) & 1]);
         } else if (j + 1 < n_tiles) {
           // statistics and first chunk of the next tile (its product does not depend on this fold)
           ok = advance_stats(j + 1);
           ok = ok && __all_sync(0xffffffffu, mbar_wait_bounded(bars.pv_done((j + 1) % NP), ((j + 1) / NP) & 1, abort_flag, W_DQ_O));
           if (ok) {
             tc_fence_after();
-            tmem_ld16(lane_addr + C::COL_O + ((j + 1) % NO) * D + col0, obuf[(ch + 1) & 1]);
+            tmem_ldN<CH>(lane_addr + C::COL_O + ((j + 1) % NO) * D + col0, obuf[(ch + 1) & 1]);
           }
         }
-        if (O_MAGIC) tmem_arm(o_addr + ch * 16, 16);
+        if (O_MAGIC) tmem_arm(o_addr + ch * CH, CH);
         const uint32_t* o = obuf[ch & 1];
         if (DUMP && dumping && j == 0) {
           uint32_t* dp = reinterpret_cast<uint32_t*>(static_cast<char*>(prm.dump) + kQTile * kKeyTile * 5);
 #pragma unroll
-          for (int i = 0; i < 16; ++i) dp[row * D + col0 + ch * 16 + i] = O_MAGIC ? o[i] - kMagicBits : o[i];
+          for (int i = 0; i < CH; ++i) dp[row * D + col0 + ch * CH + i] = O_MAGIC ? o[i] - kMagicBits : o[i];
         }
 #pragma unroll
-        for (int i = 0; i < 8; ++i) {
+        for (int i = 0; i < CH / 2; ++i) {
           float2 y = make_float2(__uint_as_float(o[2 * i]), __uint_as_float(o[2 * i + 1]));
           if (ALGO == kPiper && !O_MAGIC) y = make_float2(__uint_as_float(o[2 * i] + kMagicBits), __uint_as_float(o[2 * i + 1] + kMagicBits));
           if (ALGO == kPiper) {
             // the word is the float 1.5*2^23 + partial; num += partial * c
-            num2[ch * 8 + i] = __ffma2_rn(__fadd2_rn(y, neg_magic2), c2, num2[ch * 8 + i]);
+            num2[ch * (CH / 2) + i] = __ffma2_rn(__fadd2_rn(y, neg_magic2), c2, num2[ch * (CH / 2) + i]);
           } else {
-            num2[ch * 8 + i] = __fadd2_rn(num2[ch * 8 + i], __half22float2(__floats2half2_rn(y.x, y.y)));
+            num2[ch * (CH / 2) + i] = __fadd2_rn(num2[ch * (CH / 2) + i], __half22float2(__floats2half2_rn(y.x, y.y)));
           }
         }
       }

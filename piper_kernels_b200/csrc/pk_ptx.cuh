@@ -188,6 +188,12 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t* r) {
       : "r"(taddr)
       : "memory");
 }
+template <int N>
+__device__ __forceinline__ void tmem_ldN(uint32_t taddr, uint32_t* r) {
+  static_assert(N == 16 || N == 32, "supported widths");
+  if (N == 16) tmem_ld16(taddr, r);
+  else tmem_ld32(taddr, r);
+}
 __device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t* r) {
   asm volatile(
       "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], "

@@ -31,26 +31,35 @@ def capture(call: AttentionCall, bh: int, q_tile: int, max_tiles: int = 1024) ->
 
 
 def summarize(tr: np.ndarray, n_tiles: int, nswg: int) -> str:
+    """Average cycles per key tile, per role.  Stamp slots: softmax 0 start, 1 scores ready,
+    4 scores in registers, 2 tile max known / score buffer released, 5 codes computed,
+    6 probability buffer free, 7 probabilities stored, 3 published; dequant 0 start, 1 rescaled,
+    2 first chunk loaded, 6 all chunks folded, 3 buffer released; issue warps 0 start, 1 operands
+    ready, 2 issued."""
     n = min(n_tiles, tr.shape[1])
     t0 = tr[tr > 0].min()
     tr = np.where(tr > 0, tr - t0, -1)[:, :n]
     lo, hi = min(8, n // 4), n - 2
+    d = lambda x, a, b: float(np.mean(x[:, b] - x[:, a]))  # noqa: E731
     lines = [f"tiles {n}; total {int(tr.max())} cycles; steady-state period {(tr[2, hi, 3] - tr[2, lo, 3]) / (hi - lo):.0f} cycles per tile"]
     for w in range(nswg):
         x = tr[w, lo + ((w - lo) % nswg):hi:nswg]
-        lines.append(f"softmax{w}: wait {np.mean(x[:, 1] - x[:, 0]):.0f}  pass1 {np.mean(x[:, 2] - x[:, 1]):.0f}  "
-                     f"pass2+publish {np.mean(x[:, 3] - x[:, 2]):.0f}  per own tile {np.mean(np.diff(x[:, 0])):.0f}")
+        if x[:, 4].min() >= 0:  # single-pass softmax stamps
+            lines.append(f"softmax{w}: wait scores {d(x, 0, 1):.0f} | load {d(x, 1, 4):.0f} | scale+max+release {d(x, 4, 2):.0f} | "
+                         f"exp+codes {d(x, 2, 5):.0f} | wait P buffer {d(x, 5, 6):.0f} | store P {d(x, 6, 7):.0f} | publish {d(x, 7, 3):.0f} | "
+                         f"per own tile {np.mean(np.diff(x[:, 0])):.0f}")
+        else:
+            lines.append(f"softmax{w}: wait {d(x, 0, 1):.0f} | pass 1 {d(x, 1, 2):.0f} | pass 2 + publish {d(x, 2, 3):.0f} | per own tile {np.mean(np.diff(x[:, 0])):.0f}")
     x = tr[2, lo:hi]
-    lines.append(f"dequant : wait stats {np.mean(x[:, 1] - x[:, 0]):.0f}  wait PV {np.mean(x[:, 2] - x[:, 1]):.0f}  "
-                 f"fold {np.mean(x[:, 3] - x[:, 2]):.0f}  per tile {np.mean(np.diff(x[:, 0])):.0f}")
+    lines.append(f"dequant : rescale {d(x, 0, 1):.0f} | first chunk {d(x, 1, 2):.0f} | fold (incl. next tile's statistics) {d(x, 2, 6):.0f} | "
+                 f"release {d(x, 6, 3):.0f} | per tile {np.mean(np.diff(x[:, 0])):.0f}")
     for r, name in ((3, "S issue "), (4, "PV issue")):
         x = tr[r, lo:hi]
-        lines.append(f"{name}: wait {np.mean(x[:, 1] - x[:, 0]):.0f}  issue {np.mean(x[:, 2] - x[:, 1]):.0f}  per tile {np.mean(np.diff(x[:, 0])):.0f}")
+        lines.append(f"{name}: wait {d(x, 0, 1):.0f} | issue {d(x, 1, 2):.0f} | per tile {np.mean(np.diff(x[:, 0])):.0f}")
     own = np.arange(n) % nswg
     p_done = tr[own, np.arange(n), 3]
-    lines.append(f"P published -> PV issued: {np.mean(tr[4, lo:hi, 2] - p_done[lo:hi]):.0f}; "
-                 f"PV issued -> dequant starts folding: {np.mean(tr[2, lo:hi, 2] - tr[4, lo:hi, 2]):.0f}; "
-                 f"S issued -> softmax picks it up: {np.mean(tr[own, np.arange(n), 1][lo:hi] - tr[3, lo:hi, 2]):.0f}")
+    lines.append(f"P published -> PV issued {np.mean(tr[4, lo:hi, 2] - p_done[lo:hi]):.0f} | PV issued -> fold begins {np.mean(tr[2, lo:hi, 0] - tr[4, lo:hi, 2]):.0f} | "
+                 f"S issued -> softmax picks it up {np.mean(tr[own, np.arange(n), 1][lo:hi] - tr[3, lo:hi, 2]):.0f}")
     return "\n".join(lines)
 
 
