@@ -649,12 +649,15 @@ fused_attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
           tmem_ldN<CH>(o_addr + (ch + 1) * CH, obuf[(ch + 1) & 1]);
         } else if (j + 1 < n_tiles) {
           // statistics and first chunk of the next tile (its product does not depend on this fold)
+          PK_STAMP(2, j, 4);
           ok = advance_stats(j + 1);
+          PK_STAMP(2, j, 7);
           ok = ok && __all_sync(0xffffffffu, mbar_wait_bounded(bars.pv_done((j + 1) % NP), ((j + 1) / NP) & 1, abort_flag, W_DQ_O));
           if (ok) {
             tc_fence_after();
             tmem_ldN<CH>(lane_addr + C::COL_O + ((j + 1) % NO) * D + col0, obuf[(ch + 1) & 1]);
           }
+          PK_STAMP(2, j, 5);
         }
         if (O_MAGIC) tmem_arm(o_addr + ch * CH, CH);
         const uint32_t* o = obuf[ch & 1];
