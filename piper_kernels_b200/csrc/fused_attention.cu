@@ -43,6 +43,15 @@
 #ifndef PK_S_VARIANT
 #define PK_S_VARIANT 0
 #endif
+// Votes keep a warp converged around the .sync.aligned tensor-memory instructions when a wait is
+// abandoned; PK_NO_VOTES drops them (experiments only).
+#ifdef PK_NO_VOTES
+#define WARP_ALL(x) (x)
+#define WARP_ANY(x) (x)
+#else
+#define WARP_ALL(x) __all_sync(0xffffffffu, (x))
+#define WARP_ANY(x) __any_sync(0xffffffffu, (x))
+#endif
 #ifndef PK_DQ_CHUNK
 #define PK_DQ_CHUNK 16
 #endif
@@ -336,8 +345,8 @@ fused_attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
     for (int j = wg; j < n_tiles; j += NSWG) {
       PK_STAMP(wg, j, 0);
       // votes keep the warp converged for the .sync.aligned tensor-memory ops even when a wait is abandoned
-      if (!__all_sync(0xffffffffu, mbar_wait_bounded(bars.vec_full(j % NVEC), (j / NVEC) & 1, abort_flag, W_SM_VEC))) break;
-      if (!__all_sync(0xffffffffu, mbar_wait_bounded(bars.qk_done(j % NK), (j / NK) & 1, abort_flag, W_SM_S))) break;
+      if (!WARP_ALL(mbar_wait_bounded(bars.vec_full(j % NVEC), (j / NVEC) & 1, abort_flag, W_SM_VEC))) break;
+      if (!WARP_ALL(mbar_wait_bounded(bars.qk_done(j % NK), (j / NK) & 1, abort_flag, W_SM_S))) break;
       tc_fence_after();
       PK_STAMP(wg, j, 1);
       const uint32_t s_addr = lane_addr + C::COL_S + (j % NS) * kKeyTile;
@@ -428,6 +437,9 @@ fused_attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
       uint32_t packed[kKeyTile / 4];
 #pragma unroll
       for (int c4 = 0; c4 < kKeyTile / 4; ++c4) {
+#ifdef PK_SM_YIELD
+        if ((c4 & 3) == 3) __nanosleep(PK_SM_YIELD);
+#endif
         const float2 d0 = __fadd2_rn(t2[c4 * 2 + 0], shift2), d1 = __fadd2_rn(t2[c4 * 2 + 1], shift2);
         const float2 e0 = make_float2(ex2_approx(d0.x), ex2_approx(d0.y));
         const float2 e1 = make_float2(ex2_approx(d1.x), ex2_approx(d1.y));
@@ -449,7 +461,7 @@ fused_attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
       }
       PK_STAMP(wg, j, 5);
       // probability buffer j%NP was last read by the PV product of tile j-NP
-      if (j >= NP && !__all_sync(0xffffffffu, mbar_wait_bounded(bars.pv_done(j % NP), ((j / NP) - 1) & 1, abort_flag, W_SM_PV))) break;
+      if (j >= NP && !WARP_ALL(mbar_wait_bounded(bars.pv_done(j % NP), ((j / NP) - 1) & 1, abort_flag, W_SM_PV))) break;
       tc_fence_after();
       PK_STAMP(wg, j, 6);
       const uint32_t p_addr = lane_addr + C::COL_P + (j % NP) * (kKeyTile / 4);
@@ -500,7 +512,7 @@ fused_attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
       PK_STAMP(wg, j, 2);
 
       // probability buffer j%NP was last read by the PV product of tile j-NP
-      if (j >= NP && !__all_sync(0xffffffffu, mbar_wait_bounded(bars.pv_done(j % NP), ((j / NP) - 1) & 1, abort_flag, W_SM_PV))) break;
+      if (j >= NP && !WARP_ALL(mbar_wait_bounded(bars.pv_done(j % NP), ((j / NP) - 1) & 1, abort_flag, W_SM_PV))) break;
       tc_fence_after();
       const uint32_t p_addr = lane_addr + C::COL_P + (j % NP) * (kKeyTile / 4);
 
@@ -597,7 +609,7 @@ fused_attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
     // on the published per-tile statistics, so it is evaluated one tile ahead of the fold.
     float ow = 1.f, c = 0.f;
     auto advance_stats = [&](int j) -> bool {
-      if (!__all_sync(0xffffffffu, mbar_wait_bounded(bars.stat_full(j % NSTAT), (j / NSTAT) & 1, abort_flag, W_DQ_STAT))) return false;
+      if (!WARP_ALL(mbar_wait_bounded(bars.stat_full(j % NSTAT), (j / NSTAT) & 1, abort_flag, W_DQ_STAT))) return false;
       const float2 st = stat_ring[(j % NSTAT) * kQTile + row];
       if (ALGO == kPiper) {
         const float bm = st.x;
@@ -625,7 +637,7 @@ fused_attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
     const float2 neg_magic2 = make_float2(-kMagic, -kMagic);
     if (n_tiles > 0) {
       ok = advance_stats(0);
-      ok = ok && __all_sync(0xffffffffu, mbar_wait_bounded(bars.pv_done(0), 0, abort_flag, W_DQ_O));
+      ok = ok && WARP_ALL(mbar_wait_bounded(bars.pv_done(0), 0, abort_flag, W_DQ_O));
       if (ok) {
         tc_fence_after();
         tmem_ldN<CH>(lane_addr + C::COL_O + col0, obuf[0]);
@@ -634,7 +646,7 @@ fused_attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
     for (int j = 0; ok && j < n_tiles; ++j) {
       PK_STAMP(2, j, 0);
       const uint32_t o_addr = lane_addr + C::COL_O + (j % NO) * D + col0;
-      if (__any_sync(0xffffffffu, ow != 1.f)) {
+      if (WARP_ANY(ow != 1.f)) {
         const float2 ow2 = make_float2(ow, ow);
 #pragma unroll
         for (int d = 0; d < DH / 2; ++d) num2[d] = __fmul2_rn(num2[d], ow2);
@@ -652,7 +664,7 @@ fused_attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
           PK_STAMP(2, j, 4);
           ok = advance_stats(j + 1);
           PK_STAMP(2, j, 7);
-          ok = ok && __all_sync(0xffffffffu, mbar_wait_bounded(bars.pv_done((j + 1) % NP), ((j + 1) / NP) & 1, abort_flag, W_DQ_O));
+          ok = ok && WARP_ALL(mbar_wait_bounded(bars.pv_done((j + 1) % NP), ((j + 1) / NP) & 1, abort_flag, W_DQ_O));
           if (ok) {
             tc_fence_after();
             tmem_ldN<CH>(lane_addr + C::COL_O + ((j + 1) % NO) * D + col0, obuf[(ch + 1) & 1]);
