@@ -58,6 +58,10 @@
 #ifndef PK_NDQ
 #define PK_NDQ 1
 #endif
+// chunk of the fold after which the dequant warpgroup evaluates the next tile's factors
+#ifndef PK_DQ_STAT_AT
+#define PK_DQ_STAT_AT 1
+#endif
 #ifndef PK_NSWG_PIPER
 #define PK_NSWG_PIPER 2
 #endif
@@ -118,11 +122,13 @@ struct Cfg {
   static constexpr int OFF_BAR = OFF_STAT + NSTAT * kQTile * 8;
   static constexpr int NUM_BARS = 1 + 2 * NK + NV + NVEC + NS + 2 * NP + NO + NSTAT;
   static constexpr int OFF_MISC = OFF_BAR + NUM_BARS * 8;
-  static constexpr int SMEM_BYTES = OFF_MISC + 16 + 1024;  // + slack for 1024-byte alignment
+  static constexpr int OFF_MAGIC = OFF_MISC + 16;           // 16 words holding the arming pattern
+  static constexpr int SMEM_BYTES = OFF_MAGIC + 64 + 1024;  // + slack for 1024-byte alignment
   static constexpr uint32_t COL_S = 0;
   static constexpr uint32_t COL_P = NS * kKeyTile;
   static constexpr uint32_t COL_O = COL_P + NP * (kKeyTile / 4);
   static_assert(COL_O + NO * D <= TMEM_COLS, "tensor memory budget");
+  static_assert(OFF_MAGIC % 16 == 0, "the arming block is read with 16-byte loads");
 };
 
 // shared-memory addresses of the mbarriers.  One commit per product: qk_done[j % NK] is
@@ -175,6 +181,17 @@ __device__ __forceinline__ void tmem_arm(uint32_t addr, int ncols) {
   for (int c = 0; c < ncols; c += 16) tmem_st16(addr + c, m);
 }
 
+// Sixteen registers holding the arming pattern, read from shared memory so that the compiler
+// treats them as sixteen live values (one consecutive block that every arming store re-uses)
+// instead of re-creating sixteen constants in front of each store.
+__device__ __forceinline__ void load_arm_block(uint32_t smem_addr, uint32_t* m) {
+#pragma unroll
+  for (int i = 0; i < 4; ++i)
+    asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(m[4 * i]), "=r"(m[4 * i + 1]), "=r"(m[4 * i + 2]), "=r"(m[4 * i + 3])
+                 : "r"(smem_addr + 16 * i));
+}
+
 template <int D, int ALGO, bool K_PER_BLOCK, int DEBUG>
 __global__ void __launch_bounds__(Cfg<D, ALGO>::THREADS, 1)
 fused_attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
@@ -221,6 +238,7 @@ fused_attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
     *abort_flag = 0;
     fence_barrier_init();
   }
+  if (tid < 16) reinterpret_cast<volatile uint32_t*>(smem + C::OFF_MAGIC)[tid] = kMagicBits;
   constexpr int PROD_WARP = (NSWG + C::NDQ) * 4;
   constexpr int QK_WARP = PROD_WARP + 1;
   constexpr int PV_WARP = PROD_WARP + 2;
@@ -342,6 +360,8 @@ fused_attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
     // then probabilities), which keeps the loop body small enough for the instruction cache
     // that three different roles share; the chunk after the current one is always in flight.
     const float2 neg_magic2 = make_float2(-kMagic, -kMagic);
+    uint32_t armv[16];
+    load_arm_block(smem_base + C::OFF_MAGIC, armv);
     for (int j = wg; j < n_tiles; j += NSWG) {
       PK_STAMP(wg, j, 0);
       // votes keep the warp converged for the .sync.aligned tensor-memory ops even when a wait is abandoned
@@ -406,7 +426,8 @@ fused_attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
 #pragma unroll
       for (int c = 0; c < kKeyTile; ++c) sraw[c] += kMagicBits;
 #else
-      tmem_arm(s_addr, kKeyTile);
+#pragma unroll
+      for (int c16 = 0; c16 < kKeyTile; c16 += 16) tmem_st16(s_addr + c16, armv);
 #endif
       float2 t2[kKeyTile / 2];
 #pragma unroll
@@ -435,14 +456,25 @@ fused_attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
       const float2 c255 = make_float2(255.f, 255.f), magic2 = make_float2(kMagic, kMagic);
       float2 psum_a = make_float2(0.f, 0.f), psum_b = make_float2(0.f, 0.f);
       uint32_t packed[kKeyTile / 4];
+#ifdef PK_SM_EARLY_P
+      // probability buffer j%NP was last read by the PV product of tile j-NP; it is waited for
+      // here so that the codes can be stored four words at a time as they are produced
+      if (j >= NP && !WARP_ALL(mbar_wait_bounded(bars.pv_done(j % NP), ((j / NP) - 1) & 1, abort_flag, W_SM_PV))) break;
+      tc_fence_after();
+      const uint32_t p_addr = lane_addr + C::COL_P + (j % NP) * (kKeyTile / 4);
+#endif
 #pragma unroll
       for (int c4 = 0; c4 < kKeyTile / 4; ++c4) {
 #ifdef PK_SM_YIELD
         if ((c4 & 3) == 3) __nanosleep(PK_SM_YIELD);
 #endif
         const float2 d0 = __fadd2_rn(t2[c4 * 2 + 0], shift2), d1 = __fadd2_rn(t2[c4 * 2 + 1], shift2);
+#if defined(PK_EXP) && (PK_EXP & 8)
+        const float2 e0 = d0, e1 = d1;
+#else
         const float2 e0 = make_float2(ex2_approx(d0.x), ex2_approx(d0.y));
         const float2 e1 = make_float2(ex2_approx(d1.x), ex2_approx(d1.y));
+#endif
         if (ALGO == kPiper) {
           const float4 inv = vk[2 * (kKeyTile / 4) + c4];
           psum_a = __ffma2_rn(e0, make_float2(inv.x, inv.y), psum_a);
@@ -458,14 +490,21 @@ fused_attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
           const uint32_t hi = __nv_cvt_float2_to_fp8x2(e1, __NV_SATFINITE, __NV_E4M3);
           packed[c4] = __byte_perm(lo, hi, 0x5410);
         }
+#ifdef PK_SM_EARLY_P
+        if ((c4 & 3) == 3) tmem_st4(p_addr + (c4 & ~3), packed + (c4 & ~3));
+#endif
       }
       PK_STAMP(wg, j, 5);
+#ifndef PK_SM_EARLY_P
       // probability buffer j%NP was last read by the PV product of tile j-NP
       if (j >= NP && !WARP_ALL(mbar_wait_bounded(bars.pv_done(j % NP), ((j / NP) - 1) & 1, abort_flag, W_SM_PV))) break;
       tc_fence_after();
       PK_STAMP(wg, j, 6);
       const uint32_t p_addr = lane_addr + C::COL_P + (j % NP) * (kKeyTile / 4);
       tmem_st16(p_addr, packed);
+#else
+      PK_STAMP(wg, j, 6);
+#endif
       if (DUMP) {
         if (dumping && j == 0) {
           uint32_t* dp = reinterpret_cast<uint32_t*>(static_cast<char*>(prm.dump) + kQTile * kKeyTile * 4);
@@ -605,9 +644,12 @@ fused_attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
     for (int d = 0; d < DH / 2; ++d) num2[d] = make_float2(0.f, 0.f);
     float den = 0.f, m = -INFINITY;
     bool ok = true;
-    // Row statistics recurrence (running max, denominator, rescale factors); it depends only
-    // on the published per-tile statistics, so it is evaluated one tile ahead of the fold.
-    float ow = 1.f, c = 0.f;
+    // Row statistics recurrence (running max, denominator, rescale factors).  It depends only on
+    // the per-tile statistics that the softmax warpgroups publish several tiles ahead, so the
+    // factors of tile j+1 are evaluated early in the fold of tile j, where the chain of dependent
+    // instructions (shared-memory load, two exponentials) overlaps the fold arithmetic.
+    float ow = 1.f, c = 0.f;      // factors of the tile being folded
+    float ow_n = 1.f, c_n = 0.f;  // factors of the next tile
     auto advance_stats = [&](int j) -> bool {
       if (!WARP_ALL(mbar_wait_bounded(bars.stat_full(j % NSTAT), (j / NSTAT) & 1, abort_flag, W_DQ_STAT))) return false;
       const float2 st = stat_ring[(j % NSTAT) * kQTile + row];
@@ -615,26 +657,31 @@ fused_attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
         const float bm = st.x;
         const float nm = fmaxf(m, bm);
         float cw;
-        if (nm == -INFINITY) { ow = 1.f; cw = 0.f; }
+        if (nm == -INFINITY) { ow_n = 1.f; cw = 0.f; }
         else {
-          ow = (m == nm) ? 1.f : ex2_approx(m - nm);
+          ow_n = (m == nm) ? 1.f : ex2_approx(m - nm);
           cw = (bm == nm) ? 1.f : ex2_approx(bm - nm);
         }
-        den = fmaf(den, ow, st.y * cw);
-        c = cw * (1.f / 255.f);
+        den = fmaf(den, ow_n, st.y * cw);
+        c_n = cw * (1.f / 255.f);
         m = nm;
       } else {
-        ow = st.x;
-        den = fmaf(den, ow, st.y);
-        c = 1.f;
+        ow_n = st.x;
+        den = fmaf(den, ow_n, st.y);
+        c_n = 1.f;
       }
       return true;
     };
-    // The partial is read 16 columns at a time; the next chunk's load is always in flight while
+    // The partial is read CH columns at a time; the next chunk's load is always in flight while
     // the current one is folded, across tile boundaries too: the first chunk of tile j+1 is
     // requested before the last chunk of tile j is folded.  Each chunk is re-armed once read.
+    constexpr int NCH = DH / CH;
+    static_assert(NCH >= 2, "the next tile's product is waited for before the last chunk");
+    constexpr int STAT_AT = (NCH > 2) ? PK_DQ_STAT_AT : 0;  // chunk after which the next tile's factors are evaluated
     uint32_t obuf[2][CH];
     const float2 neg_magic2 = make_float2(-kMagic, -kMagic);
+    uint32_t armv[16];
+    load_arm_block(smem_base + C::OFF_MAGIC, armv);
     if (n_tiles > 0) {
       ok = advance_stats(0);
       ok = ok && WARP_ALL(mbar_wait_bounded(bars.pv_done(0), 0, abort_flag, W_DQ_O));
@@ -645,6 +692,7 @@ fused_attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
     }
     for (int j = 0; ok && j < n_tiles; ++j) {
       PK_STAMP(2, j, 0);
+      ow = ow_n; c = c_n;
       const uint32_t o_addr = lane_addr + C::COL_O + (j % NO) * D + col0;
       if (WARP_ANY(ow != 1.f)) {
         const float2 ow2 = make_float2(ow, ow);
@@ -654,25 +702,38 @@ fused_attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
       const float2 c2 = make_float2(c, c);
       PK_STAMP(2, j, 1);
 #pragma unroll
-      for (int ch = 0; ch < DH / CH; ++ch) {
+      for (int ch = 0; ch < NCH; ++ch) {
         tmem_wait_ld();
         if (ch == 0) PK_STAMP(2, j, 2);
-        if (ch + 1 < DH / CH) {
+        if (ch + 1 < NCH) {
           tmem_ldN<CH>(o_addr + (ch + 1) * CH, obuf[(ch + 1) & 1]);
-        } else if (j + 1 < n_tiles) {
-          // statistics and first chunk of the next tile (its product does not depend on this fold)
+        } else if (j + 1 < n_tiles && ok) {
+          // first chunk of the next tile (its product was waited for below, chunks ago)
+          tmem_ldN<CH>(lane_addr + C::COL_O + ((j + 1) % NO) * D + col0, obuf[(ch + 1) & 1]);
+        }
+        if (ch == STAT_AT && j + 1 < n_tiles) {
           PK_STAMP(2, j, 4);
           ok = advance_stats(j + 1);
           PK_STAMP(2, j, 7);
           ok = ok && WARP_ALL(mbar_wait_bounded(bars.pv_done((j + 1) % NP), ((j + 1) / NP) & 1, abort_flag, W_DQ_O));
-          if (ok) {
-            tc_fence_after();
-            tmem_ldN<CH>(lane_addr + C::COL_O + ((j + 1) % NO) * D + col0, obuf[(ch + 1) & 1]);
-          }
+          tc_fence_after();
           PK_STAMP(2, j, 5);
         }
-        if (O_MAGIC) tmem_arm(o_addr + ch * CH, CH);
+#if defined(PK_EXP) && (PK_EXP & 2)
+        if (false) {
+#else
+        if (O_MAGIC) {
+#endif
+#pragma unroll
+          for (int c16 = 0; c16 < CH; c16 += 16) tmem_st16(o_addr + ch * CH + c16, armv);
+        }
         const uint32_t* o = obuf[ch & 1];
+#if defined(PK_EXP) && (PK_EXP & 1)
+        if (ch >= 1) continue;
+#endif
+#if defined(PK_EXP) && (PK_EXP & 4)
+        if (ch >= NCH / 2) continue;
+#endif
         if (DUMP && dumping && j == 0) {
           uint32_t* dp = reinterpret_cast<uint32_t*>(static_cast<char*>(prm.dump) + kQTile * kKeyTile * 5);
 #pragma unroll

@@ -34,8 +34,8 @@ def summarize(tr: np.ndarray, n_tiles: int, nswg: int) -> str:
     """Average cycles per key tile, per role.  Stamp slots: softmax 0 start, 1 scores ready,
     4 scores in registers, 2 tile max known / score buffer released, 5 codes computed,
     6 probability buffer free, 7 probabilities stored, 3 published; dequant 0 start, 1 rescaled,
-    2 first chunk loaded, 4 last chunk loaded, 7 next statistics done, 5 next tile's first load
-    issued, 6 all chunks folded, 3 buffer released; issue warps 0 start, 1 operands
+    2 first chunk loaded, 4 early chunks folded, 7 next statistics done, 5 next tile's product
+    complete, 6 all chunks folded, 3 buffer released; issue warps 0 start, 1 operands
     ready, 2 issued."""
     n = min(n_tiles, tr.shape[1])
     t0 = tr[tr > 0].min()
@@ -52,8 +52,8 @@ def summarize(tr: np.ndarray, n_tiles: int, nswg: int) -> str:
         else:
             lines.append(f"softmax{w}: wait {d(x, 0, 1):.0f} | pass 1 {d(x, 1, 2):.0f} | pass 2 + publish {d(x, 2, 3):.0f} | per own tile {np.mean(np.diff(x[:, 0])):.0f}")
     x = tr[2, lo:hi]
-    lines.append(f"dequant : rescale {d(x, 0, 1):.0f} | first chunk {d(x, 1, 2):.0f} | chunks before the last {d(x, 2, 4):.0f} | "
-                 f"next tile's statistics {d(x, 4, 7):.0f} | next tile's product + first load {d(x, 7, 5):.0f} | last chunk {d(x, 5, 6):.0f} | "
+    lines.append(f"dequant : rescale {d(x, 0, 1):.0f} | first chunk {d(x, 1, 2):.0f} | early chunks {d(x, 2, 4):.0f} | "
+                 f"next tile's statistics {d(x, 4, 7):.0f} | next tile's product wait {d(x, 7, 5):.0f} | remaining chunks {d(x, 5, 6):.0f} | "
                  f"release {d(x, 6, 3):.0f} | per tile {np.mean(np.diff(x[:, 0])):.0f}")
     for r, name in ((3, "S issue "), (4, "PV issue")):
         x = tr[r, lo:hi]
