@@ -15,7 +15,7 @@
 //   dequant warpgroup     thread = query row; holds the FP32 numerator row, folds every 64-key
 //                         PV partial into it, owns the running max / denominator, writes out
 //   producer warp         TMA loads of the Q tile, K tiles, V^T tiles and per-key vectors
-//   mma warp              one thread issues tcgen05.mma: S = Q K^T (SS form, kind::i8) and
+//   two issue warps       one thread each issues tcgen05.mma: S = Q K^T (SS form, kind::i8) and
 //                         O_part = P V (A from tensor memory; kind::i8 U8xS8 or kind::f8f6f4)
 // Piper's probability codes depend only on the tile's own maximum, so two softmax warpgroups
 // process alternate key tiles in parallel; Sage's depend on the running maximum, so it uses one.
@@ -37,21 +37,10 @@
 #include "pk_internal.h"
 #include "pk_ptx.cuh"
 
-#ifndef PK_SOFTMAX_UNROLLED
-#define PK_SOFTMAX_UNROLLED 1
-#endif
-#ifndef PK_S_VARIANT
-#define PK_S_VARIANT 0
-#endif
 // Votes keep a warp converged around the .sync.aligned tensor-memory instructions when a wait is
-// abandoned; PK_NO_VOTES drops them (experiments only).
-#ifdef PK_NO_VOTES
-#define WARP_ALL(x) (x)
-#define WARP_ANY(x) (x)
-#else
+// abandoned.
 #define WARP_ALL(x) __all_sync(0xffffffffu, (x))
 #define WARP_ANY(x) __any_sync(0xffffffffu, (x))
-#endif
 #ifndef PK_DQ_CHUNK
 #define PK_DQ_CHUNK 16
 #endif
@@ -79,7 +68,14 @@ constexpr int NK = 8;      // K tile ring
 constexpr int NV = 4;      // V^T tile ring
 constexpr int NVEC = 16;   // per-key vector ring (k_mul, k_add, k_inv: 3 x 64 floats)
 constexpr int NSTAT = 8;   // softmax -> dequant per-row statistics ring
-constexpr int NS = 3;      // score buffers in tensor memory
+// sage runs 384 threads (168 registers each at launch): softmax / dequant 232 / helpers 48
+#ifndef PK_REG_SM_SAGE
+#define PK_REG_SM_SAGE 152
+#endif
+#ifndef PK_NS
+#define PK_NS 3
+#endif
+constexpr int NS = PK_NS;  // score buffers in tensor memory
 constexpr int NP = 4;      // probability buffers in tensor memory
 constexpr int NO = 2;      // PV partial buffers in tensor memory
 constexpr int V_LAG = 4;   // the producer issues V^T tile j together with K tile j + V_LAG
@@ -121,7 +117,7 @@ struct Cfg {
   static constexpr int OFF_STAT = OFF_VEC + NVEC * VEC_FLOATS * 4;
   static constexpr int OFF_BAR = OFF_STAT + NSTAT * kQTile * 8;
   static constexpr int NUM_BARS = 1 + 2 * NK + NV + NVEC + NS + 2 * NP + NO + NSTAT;
-  static constexpr int OFF_MISC = OFF_BAR + NUM_BARS * 8;
+  static constexpr int OFF_MISC = (OFF_BAR + NUM_BARS * 8 + 15) / 16 * 16;
   static constexpr int OFF_MAGIC = OFF_MISC + 16;           // 16 words holding the arming pattern
   static constexpr int SMEM_BYTES = OFF_MAGIC + 64 + 1024;  // + slack for 1024-byte alignment
   static constexpr uint32_t COL_S = 0;
@@ -200,11 +196,7 @@ fused_attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
   constexpr int NSWG = C::NSWG;
   constexpr bool DUMP = DEBUG == 1;      // copy out the first key tile's intermediates
   constexpr bool TIMELINE = DEBUG == 2;  // per-role clock stamps of one CTA
-#ifdef PK_NO_O_MAGIC
-  constexpr bool O_MAGIC = false;
-#else
   constexpr bool O_MAGIC = (ALGO == kPiper);  // the sage partial is FP32 and needs no conversion
-#endif
   extern __shared__ uint8_t smem_raw[];
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t* smem = smem_raw + (smem_base - smem_u32(smem_raw));
@@ -313,7 +305,7 @@ fused_attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
         const uint64_t kdesc = kdesc0 + static_cast<uint64_t>(((j % NK) * C::K_BYTES) >> 4);
         const uint32_t d = tmem_base + C::COL_S + (j % NS) * kKeyTile;
 #pragma unroll
-        for (int kk = 0; kk < D / 32; ++kk) umma_i8_ss(d, qdesc + 2 * kk, kdesc + 2 * kk, idesc_qk, (PK_S_VARIANT == 2 && kk == 0) ? 0u : 1u);
+        for (int kk = 0; kk < D / 32; ++kk) umma_i8_ss(d, qdesc + 2 * kk, kdesc + 2 * kk, idesc_qk, 1u);
         tc_commit(bars.qk_done(j % NK));
         PK_STAMP(3, j, 2);
       }
@@ -345,7 +337,7 @@ fused_attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
     }
   } else if (wg < NSWG) {
     // ------------------------------------------------------------------ softmax
-    if (ALGO == kPiper) { if (PK_REG_SM <= C::LAUNCH_REGS) setmaxnreg_dec<PK_REG_SM>(); else setmaxnreg_inc<PK_REG_SM>(); } else setmaxnreg_dec<128>();
+    if (ALGO == kPiper) { if (PK_REG_SM <= C::LAUNCH_REGS) setmaxnreg_dec<PK_REG_SM>(); else setmaxnreg_inc<PK_REG_SM>(); } else setmaxnreg_dec<PK_REG_SM_SAGE>();
     const int row = tid & 127;
     const uint32_t lane_addr = tmem_base + (static_cast<uint32_t>((warp & 3) * 32) << 16);
     const float qm = prm.q_mul[static_cast<long long>(bh) * prm.sq_pad + q0 + row];
@@ -356,9 +348,6 @@ fused_attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
       tc_fence_before();
       for (int i = 0; i < NS; ++i) mbar_arrive(bars.s_free(i));
     }
-    // The tile is processed 16 columns at a time in two rolled passes over tensor memory (max,
-    // then probabilities), which keeps the loop body small enough for the instruction cache
-    // that three different roles share; the chunk after the current one is always in flight.
     const float2 neg_magic2 = make_float2(-kMagic, -kMagic);
     uint32_t armv[16];
     load_arm_block(smem_base + C::OFF_MAGIC, armv);
@@ -411,7 +400,6 @@ fused_attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
         }
       };
 
-#if PK_SOFTMAX_UNROLLED
       // Single pass over registers: the whole 64-column tile is loaded once, the score buffer is
       // re-armed and returned immediately, and t stays in registers between max and exp.
       uint32_t sraw[kKeyTile];
@@ -419,16 +407,8 @@ fused_attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
       tmem_ld32(s_addr + 32, sraw + 32);
       tmem_wait_ld();
       PK_STAMP(wg, j, 4);
-#if PK_S_VARIANT == 2
-      // no re-arming: the score buffer is free as soon as it has been read
-      tc_fence_before();
-      mbar_arrive(bars.s_free(j % NS));
-#pragma unroll
-      for (int c = 0; c < kKeyTile; ++c) sraw[c] += kMagicBits;
-#else
 #pragma unroll
       for (int c16 = 0; c16 < kKeyTile; c16 += 16) tmem_st16(s_addr + c16, armv);
-#endif
       float2 t2[kKeyTile / 2];
 #pragma unroll
       for (int ch = 0; ch < kKeyTile / 16; ++ch) scores16(sraw + ch * 16, ch, t2 + ch * 8);
@@ -436,11 +416,9 @@ fused_attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
 #pragma unroll
       for (int c2 = 2; c2 < kKeyTile / 2; c2 += 2) { bm0 = max3(bm0, t2[c2].x, t2[c2].y); bm1 = max3(bm1, t2[c2 + 1].x, t2[c2 + 1].y); }
       const float bm = fmaxf(bm0, bm1);
-#if PK_S_VARIANT == 0
       tmem_wait_st();
       tc_fence_before();
       mbar_arrive(bars.s_free(j % NS));
-#endif
       PK_STAMP(wg, j, 2);
       float shift, ow = 1.f;
       if (ALGO == kPiper) {
@@ -456,25 +434,11 @@ fused_attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
       const float2 c255 = make_float2(255.f, 255.f), magic2 = make_float2(kMagic, kMagic);
       float2 psum_a = make_float2(0.f, 0.f), psum_b = make_float2(0.f, 0.f);
       uint32_t packed[kKeyTile / 4];
-#ifdef PK_SM_EARLY_P
-      // probability buffer j%NP was last read by the PV product of tile j-NP; it is waited for
-      // here so that the codes can be stored four words at a time as they are produced
-      if (j >= NP && !WARP_ALL(mbar_wait_bounded(bars.pv_done(j % NP), ((j / NP) - 1) & 1, abort_flag, W_SM_PV))) break;
-      tc_fence_after();
-      const uint32_t p_addr = lane_addr + C::COL_P + (j % NP) * (kKeyTile / 4);
-#endif
 #pragma unroll
       for (int c4 = 0; c4 < kKeyTile / 4; ++c4) {
-#ifdef PK_SM_YIELD
-        if ((c4 & 3) == 3) __nanosleep(PK_SM_YIELD);
-#endif
         const float2 d0 = __fadd2_rn(t2[c4 * 2 + 0], shift2), d1 = __fadd2_rn(t2[c4 * 2 + 1], shift2);
-#if defined(PK_EXP) && (PK_EXP & 8)
-        const float2 e0 = d0, e1 = d1;
-#else
         const float2 e0 = make_float2(ex2_approx(d0.x), ex2_approx(d0.y));
         const float2 e1 = make_float2(ex2_approx(d1.x), ex2_approx(d1.y));
-#endif
         if (ALGO == kPiper) {
           const float4 inv = vk[2 * (kKeyTile / 4) + c4];
           psum_a = __ffma2_rn(e0, make_float2(inv.x, inv.y), psum_a);
@@ -490,21 +454,14 @@ fused_attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
           const uint32_t hi = __nv_cvt_float2_to_fp8x2(e1, __NV_SATFINITE, __NV_E4M3);
           packed[c4] = __byte_perm(lo, hi, 0x5410);
         }
-#ifdef PK_SM_EARLY_P
-        if ((c4 & 3) == 3) tmem_st4(p_addr + (c4 & ~3), packed + (c4 & ~3));
-#endif
       }
       PK_STAMP(wg, j, 5);
-#ifndef PK_SM_EARLY_P
       // probability buffer j%NP was last read by the PV product of tile j-NP
       if (j >= NP && !WARP_ALL(mbar_wait_bounded(bars.pv_done(j % NP), ((j / NP) - 1) & 1, abort_flag, W_SM_PV))) break;
       tc_fence_after();
       PK_STAMP(wg, j, 6);
       const uint32_t p_addr = lane_addr + C::COL_P + (j % NP) * (kKeyTile / 4);
       tmem_st16(p_addr, packed);
-#else
-      PK_STAMP(wg, j, 6);
-#endif
       if (DUMP) {
         if (dumping && j == 0) {
           uint32_t* dp = reinterpret_cast<uint32_t*>(static_cast<char*>(prm.dump) + kQTile * kKeyTile * 4);
@@ -518,111 +475,9 @@ fused_attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
       tmem_wait_st();
       PK_STAMP(wg, j, 7);
       tc_fence_before();
-#if PK_S_VARIANT == 1
-      mbar_arrive(bars.s_free(j % NS));
-#endif
       mbar_arrive(bars.p_ready(j % NP));
       mbar_arrive(bars.stat_full(j % NSTAT));
       PK_STAMP(wg, j, 3);
-#else
-      // ---- pass 1: tile maximum
-      uint32_t sbuf[2][16];
-      float bm0 = -INFINITY, bm1 = -INFINITY;
-      tmem_ld16(s_addr, sbuf[0]);
-#pragma unroll 1
-      for (int ch = 0; ch < kKeyTile / 16; ch += 2) {
-        float2 t2[8];
-        tmem_wait_ld();
-        tmem_ld16(s_addr + (ch + 1) * 16, sbuf[1]);
-        scores16(sbuf[0], ch, t2);
-        tmem_st16(s_addr + ch * 16, reinterpret_cast<const uint32_t*>(t2));  // pass 2 reads t, not the raw score
-#pragma unroll
-        for (int c2 = 0; c2 < 8; c2 += 2) { bm0 = max3(bm0, t2[c2].x, t2[c2].y); bm1 = max3(bm1, t2[c2 + 1].x, t2[c2 + 1].y); }
-        tmem_wait_ld();
-        if (ch + 2 < kKeyTile / 16) tmem_ld16(s_addr + (ch + 2) * 16, sbuf[0]);
-        scores16(sbuf[1], ch + 1, t2);
-        tmem_st16(s_addr + (ch + 1) * 16, reinterpret_cast<const uint32_t*>(t2));
-#pragma unroll
-        for (int c2 = 0; c2 < 8; c2 += 2) { bm0 = max3(bm0, t2[c2].x, t2[c2].y); bm1 = max3(bm1, t2[c2 + 1].x, t2[c2 + 1].y); }
-      }
-      tmem_wait_st();
-      tmem_ld16(s_addr, sbuf[0]);  // first chunk of pass 2
-      const float bm = fmaxf(bm0, bm1);
-      PK_STAMP(wg, j, 2);
-
-      // probability buffer j%NP was last read by the PV product of tile j-NP
-      if (j >= NP && !WARP_ALL(mbar_wait_bounded(bars.pv_done(j % NP), ((j / NP) - 1) & 1, abort_flag, W_SM_PV))) break;
-      tc_fence_after();
-      const uint32_t p_addr = lane_addr + C::COL_P + (j % NP) * (kKeyTile / 4);
-
-      // ---- pass 2: probabilities, 8-bit codes, denominator term
-      float shift, ow = 1.f;
-      if (ALGO == kPiper) {
-        shift = (bm == -INFINITY) ? 0.f : -bm;
-      } else {
-        const float nm = fmaxf(m_run, bm);
-        const float ns = (nm == -INFINITY) ? 0.f : nm;
-        ow = (m_run == nm) ? 1.f : ex2_approx(m_run - ns);
-        shift = 8.807354922057604f - ns;  // log2(448): P = e4m3(448 * 2^(t - max))
-        m_run = nm;
-      }
-      const float2 shift2 = make_float2(shift, shift);
-      const float2 c255 = make_float2(255.f, 255.f), magic2 = make_float2(kMagic, kMagic);
-      float2 psum_a = make_float2(0.f, 0.f), psum_b = make_float2(0.f, 0.f);
-      auto probs16 = [&](const uint32_t* sr, int ch) {
-        const float2* t2 = reinterpret_cast<const float2*>(sr);
-        uint32_t pk[4];
-#pragma unroll
-        for (int q4 = 0; q4 < 4; ++q4) {
-          const float2 d0 = __fadd2_rn(t2[q4 * 2 + 0], shift2), d1 = __fadd2_rn(t2[q4 * 2 + 1], shift2);
-          const float2 e0 = make_float2(ex2_approx(d0.x), ex2_approx(d0.y));
-          const float2 e1 = make_float2(ex2_approx(d1.x), ex2_approx(d1.y));
-          if (ALGO == kPiper) {
-            const float4 inv = vk[2 * (kKeyTile / 4) + ch * 4 + q4];
-            psum_a = __ffma2_rn(e0, make_float2(inv.x, inv.y), psum_a);
-            psum_b = __ffma2_rn(e1, make_float2(inv.z, inv.w), psum_b);
-            const float2 b0 = __ffma2_rn(e0, c255, magic2), b1 = __ffma2_rn(e1, c255, magic2);  // low byte = rne(255 e)
-            const uint32_t lo = __byte_perm(__float_as_uint(b0.x), __float_as_uint(b0.y), 0x0040);
-            const uint32_t hi = __byte_perm(__float_as_uint(b1.x), __float_as_uint(b1.y), 0x0040);
-            pk[q4] = __byte_perm(lo, hi, 0x5410);
-          } else {
-            psum_a = __fadd2_rn(psum_a, e0);
-            psum_b = __fadd2_rn(psum_b, e1);
-            const uint32_t lo = __nv_cvt_float2_to_fp8x2(e0, __NV_SATFINITE, __NV_E4M3);
-            const uint32_t hi = __nv_cvt_float2_to_fp8x2(e1, __NV_SATFINITE, __NV_E4M3);
-            pk[q4] = __byte_perm(lo, hi, 0x5410);
-          }
-        }
-        tmem_st4(p_addr + ch * 4, pk);
-        if (DUMP) {
-          if (dumping && j == 0) {
-            uint32_t* dp = reinterpret_cast<uint32_t*>(static_cast<char*>(prm.dump) + kQTile * kKeyTile * 4);
-#pragma unroll
-            for (int c = 0; c < 4; ++c) dp[row * (kKeyTile / 4) + ch * 4 + c] = pk[c];
-          }
-        }
-      };
-#pragma unroll 1
-      for (int ch = 0; ch < kKeyTile / 16; ch += 2) {
-        tmem_wait_ld();
-        tmem_ld16(s_addr + (ch + 1) * 16, sbuf[1]);
-        probs16(sbuf[0], ch);
-        tmem_wait_ld();
-        if (ch + 2 < kKeyTile / 16) tmem_ld16(s_addr + (ch + 2) * 16, sbuf[0]);
-        probs16(sbuf[1], ch + 1);
-      }
-      // hand the score buffer back re-armed, publish the probabilities and the row statistics
-      tmem_arm(s_addr, kKeyTile);
-      const float psum = (psum_a.x + psum_a.y) + (psum_b.x + psum_b.y);
-      const float2 st = (ALGO == kPiper) ? make_float2(bm, psum) : make_float2(ow, psum * (1.f / 448.f));
-      stat_ring[(j % NSTAT) * kQTile + row] = st;
-      tmem_wait_st();
-      tc_fence_before();
-      mbar_arrive(bars.s_free(j % NS));
-      mbar_arrive(bars.p_ready(j % NP));
-      mbar_arrive(bars.stat_full(j % NSTAT));
-      PK_STAMP(wg, j, 3);
-#endif
     }
   } else if (wg < NSWG + C::NDQ) {
     // ------------------------------------------------------------------ dequant + epilogue
@@ -719,21 +574,11 @@ fused_attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
           tc_fence_after();
           PK_STAMP(2, j, 5);
         }
-#if defined(PK_EXP) && (PK_EXP & 2)
-        if (false) {
-#else
         if (O_MAGIC) {
-#endif
 #pragma unroll
           for (int c16 = 0; c16 < CH; c16 += 16) tmem_st16(o_addr + ch * CH + c16, armv);
         }
         const uint32_t* o = obuf[ch & 1];
-#if defined(PK_EXP) && (PK_EXP & 1)
-        if (ch >= 1) continue;
-#endif
-#if defined(PK_EXP) && (PK_EXP & 4)
-        if (ch >= NCH / 2) continue;
-#endif
         if (DUMP && dumping && j == 0) {
           uint32_t* dp = reinterpret_cast<uint32_t*>(static_cast<char*>(prm.dump) + kQTile * kKeyTile * 5);
 #pragma unroll
@@ -742,7 +587,6 @@ fused_attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
 #pragma unroll
         for (int i = 0; i < CH / 2; ++i) {
           float2 y = make_float2(__uint_as_float(o[2 * i]), __uint_as_float(o[2 * i + 1]));
-          if (ALGO == kPiper && !O_MAGIC) y = make_float2(__uint_as_float(o[2 * i] + kMagicBits), __uint_as_float(o[2 * i + 1] + kMagicBits));
           if (ALGO == kPiper) {
             // the word is the float 1.5*2^23 + partial; num += partial * c
             num2[ch * (CH / 2) + i] = __ffma2_rn(__fadd2_rn(y, neg_magic2), c2, num2[ch * (CH / 2) + i]);

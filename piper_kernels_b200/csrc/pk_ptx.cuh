@@ -80,9 +80,6 @@ __device__ __forceinline__ bool mbar_wait_slow(uint32_t bar, uint32_t parity, vo
   uint32_t polls = 0;
   while (true) {
     if (mbar_try_wait_hint(bar, parity, 20000u)) return true;
-#ifdef PK_SPIN_SLEEP
-    if (where < 30) __nanosleep(PK_SPIN_SLEEP);  // producer / issue lanes only
-#endif
     if ((++polls & 0x3F) == 0) {
       if (*abort_flag != 0) return false;
       if (clock64() - t0 > kWaitCycleLimit) {
