@@ -188,12 +188,14 @@ __device__ __forceinline__ void load_arm_block(uint32_t smem_addr, uint32_t* m) 
                  : "r"(smem_addr + 16 * i));
 }
 
-template <int D, int ALGO, bool K_PER_BLOCK, int DEBUG>
+// CAUSAL: 0 rectangular / non-causal, 1 causal, 2 decided at run time (debug instantiations)
+template <int D, int ALGO, bool K_PER_BLOCK, int CAUSAL, int DEBUG>
 __global__ void __launch_bounds__(Cfg<D, ALGO>::THREADS, 1)
 fused_attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                        const __grid_constant__ CUtensorMap tm_v, const FusedParams prm) {
   using C = Cfg<D, ALGO>;
   constexpr int NSWG = C::NSWG;
+  const bool causal = (CAUSAL == 2) ? (prm.causal != 0) : (CAUSAL == 1);
   constexpr bool DUMP = DEBUG == 1;      // copy out the first key tile's intermediates
   constexpr bool TIMELINE = DEBUG == 2;  // per-role clock stamps of one CTA
   constexpr bool O_MAGIC = (ALGO == kPiper);  // the sage partial is FP32 and needs no conversion
@@ -209,10 +211,10 @@ fused_attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, wg = warp >> 2;
   const int bh = blockIdx.y;
   const int n_qt = prm.sq_pad / kQTile;
-  const int qt = prm.causal ? (n_qt - 1 - blockIdx.x) : blockIdx.x;  // causal: longest tiles first
+  const int qt = causal ? (n_qt - 1 - blockIdx.x) : blockIdx.x;  // causal: longest tiles first
   const int q0 = qt * kQTile;
   const int n_all = prm.sk_pad / kKeyTile;
-  const int n_tiles = prm.causal ? min(n_all, 2 * qt + 2) : n_all;
+  const int n_tiles = causal ? min(n_all, 2 * qt + 2) : n_all;
   // DUMP instantiations (debug entry point only) copy the first key tile's intermediates out
   const bool dumping = DUMP && prm.dump != nullptr && bh == prm.dump_bh && qt == prm.dump_qt;
   const bool stamping = TIMELINE && prm.timeline != nullptr && bh == prm.dump_bh && qt == prm.dump_qt &&
@@ -364,7 +366,7 @@ fused_attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
       const float4* vk = reinterpret_cast<const float4*>(vec_ring + (j % NVEC) * VEC_FLOATS);
       const float mt = K_PER_BLOCK ? qm * vec_ring[(j % NVEC) * VEC_FLOATS] : qm;
       const float2 mt2 = make_float2(mt, mt);
-      const bool diag = prm.causal && (j * kKeyTile + kKeyTile - 1 > q0);
+      const bool diag = causal && (j * kKeyTile + kKeyTile - 1 > q0);
       const int lim = q0 + row - j * kKeyTile;  // causal: columns above this index are masked
 
       // t_c = score_c * (q_mul * k_mul_c) + k_add_c for the 16 columns of chunk `ch`, two columns
@@ -684,7 +686,7 @@ int make_map(CUtensorMap* m, void* base, uint64_t rows, uint64_t cols, uint32_t 
   return PK_OK;
 }
 
-template <int D, int ALGO, bool KPB, int DEBUG>
+template <int D, int ALGO, bool KPB, int CAUSAL, int DEBUG>
 int launch_one_impl(const pk_problem& p, const Layout& L, cudaStream_t st, const DebugDump* dump) {
   using C = Cfg<D, ALGO>;
   CUtensorMap tq, tk, tv;
@@ -708,7 +710,7 @@ int launch_one_impl(const pk_problem& p, const Layout& L, cudaStream_t st, const
   prm.dump_qt = dump ? dump->q_tile : -1;
   prm.timeline = dump ? static_cast<long long*>(dump->timeline) : nullptr;
   prm.timeline_tiles = dump ? dump->timeline_tiles : 0;
-  auto kern = fused_attention_kernel<D, ALGO, KPB, DEBUG>;
+  auto kern = fused_attention_kernel<D, ALGO, KPB, CAUSAL, DEBUG>;
   {
     const cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES);
     if (e != cudaSuccess) return fail(PK_ERR_CUDA, "cudaFuncSetAttribute: %s", cuda_err(e));
@@ -722,9 +724,9 @@ int launch_one_impl(const pk_problem& p, const Layout& L, cudaStream_t st, const
 
 template <int D, int ALGO, bool KPB>
 int launch_one(const pk_problem& p, const Layout& L, cudaStream_t st, const DebugDump* dump) {
-  if (dump && dump->ptr) return launch_one_impl<D, ALGO, KPB, 1>(p, L, st, dump);
-  if (dump && dump->timeline) return launch_one_impl<D, ALGO, KPB, 2>(p, L, st, dump);
-  return launch_one_impl<D, ALGO, KPB, 0>(p, L, st, dump);
+  if (dump && dump->ptr) return launch_one_impl<D, ALGO, KPB, 2, 1>(p, L, st, dump);
+  if (dump && dump->timeline) return launch_one_impl<D, ALGO, KPB, 2, 2>(p, L, st, dump);
+  return p.is_causal ? launch_one_impl<D, ALGO, KPB, 1, 0>(p, L, st, dump) : launch_one_impl<D, ALGO, KPB, 0, 0>(p, L, st, dump);
 }
 
 template <int D, int ALGO>

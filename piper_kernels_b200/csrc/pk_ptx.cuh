@@ -41,21 +41,6 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
   return ok != 0;
 }
 
-// Same probe, but the hardware may keep the thread suspended for up to `ns` nanoseconds while the
-// phase is incomplete (it resumes as soon as the phase completes), so a waiting warp spends
-// few issue slots on polling.
-__device__ __forceinline__ bool mbar_try_wait_hint(uint32_t bar, uint32_t parity, uint32_t ns) {
-  uint32_t ok;
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
-      "selp.u32 %0, 1, 0, p;\n\t}"
-      : "=r"(ok)
-      : "r"(bar), "r"(parity), "r"(ns)
-      : "memory");
-  return ok != 0;
-}
-
 // Non-blocking probe of a phase (used where one thread polls several barriers).
 __device__ __forceinline__ bool mbar_test_wait(uint32_t bar, uint32_t parity) {
   uint32_t ok;
@@ -73,19 +58,29 @@ __device__ __forceinline__ bool mbar_test_wait(uint32_t bar, uint32_t parity) {
 constexpr long long kWaitCycleLimit = 1500000000LL;
 
 // Slow path of a wait (inlined: an out-of-line call cannot be shared by roles that run with
-// different register allocations).
+// different register allocations).  The probe loop is written in PTX so that one iteration is a
+// handful of instructions: the lanes that spin here (producer, issue warps) share their
+// scheduler with the compute warps.  Every 64 probes the abort flag and the clock are checked.
 __device__ __forceinline__ bool mbar_wait_slow(uint32_t bar, uint32_t parity, volatile int* abort_flag,
                                             int where) {
   const long long t0 = clock64();
-  uint32_t polls = 0;
   while (true) {
-    if (mbar_try_wait_hint(bar, parity, 20000u)) return true;
-    if ((++polls & 0x3F) == 0) {
-      if (*abort_flag != 0) return false;
-      if (clock64() - t0 > kWaitCycleLimit) {
-        *abort_flag = where;
-        return false;
-      }
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p, q;\n\t.reg .u32 n;\n\tmov.u32 n, 64;\n"
+        "PK_WAIT_PROBE:\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "@p bra PK_WAIT_DONE;\n\t"
+        "sub.u32 n, n, 1;\n\tsetp.ne.u32 q, n, 0;\n\t@q bra PK_WAIT_PROBE;\n"
+        "PK_WAIT_DONE:\n\tselp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    if (ok) return true;
+    if (*abort_flag != 0) return false;
+    if (clock64() - t0 > kWaitCycleLimit) {
+      *abort_flag = where;
+      return false;
     }
   }
 }

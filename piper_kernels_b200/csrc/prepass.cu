@@ -82,6 +82,7 @@ __global__ void __launch_bounds__(kThreads) colstat_partial_kernel(
   double ks[8], vs[8];
 #pragma unroll
   for (int i = 0; i < 8; ++i) ks[i] = 0.0, vs[i] = 0.0;
+#pragma unroll 4
   for (int r = r0 + rl; r < r1; r += RPP) {
     float x[8];
     if (do_k) {
@@ -164,6 +165,8 @@ __global__ void colstat_finalize_kernel(const double* __restrict__ k_part, const
 // Centred row range r[n] = max_d |v[n,d] - mean[d]|, stored as the FP32 bit pattern (the
 // values are non-negative, so unsigned integer order equals floating-point order).
 // ---------------------------------------------------------------------------------------
+constexpr int kRangePasses = 8;  // row passes per CTA of row_range_kernel
+
 template <typename T, int D, bool ALIGNED>
 __global__ void __launch_bounds__(kThreads) row_range_kernel(TensorArg v, const float* __restrict__ v_mean,
                                                              uint32_t* __restrict__ keys, int sk, int heads) {
@@ -175,17 +178,24 @@ __global__ void __launch_bounds__(kThreads) row_range_kernel(TensorArg v, const 
   float mean[8];
 #pragma unroll
   for (int i = 0; i < 8; ++i) mean[i] = v_mean[bh * D + cg * 8 + i];
-  const int r = blockIdx.x * RPP + rl;
-  float m = 0.f;
-  if (r < sk) {
-    float x[8];
-    load8<T, ALIGNED>(vp + static_cast<long long>(r) * v.ss + cg * 8, x);
+  float x[kRangePasses][8];
 #pragma unroll
-    for (int i = 0; i < 8; ++i) m = fmaxf(m, fabsf(__fsub_rn(x[i], mean[i])));
+  for (int p = 0; p < kRangePasses; ++p) {  // all loads first: kRangePasses x 16 bytes in flight per thread
+    const int r = (blockIdx.x * kRangePasses + p) * RPP + rl;
+    if (r < sk) load8<T, ALIGNED>(vp + static_cast<long long>(r) * v.ss + cg * 8, x[p]);
   }
 #pragma unroll
-  for (int o = TPR / 2; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
-  if (r < sk && cg == 0) keys[static_cast<long long>(bh) * sk + r] = __float_as_uint(m);
+  for (int p = 0; p < kRangePasses; ++p) {
+    const int r = (blockIdx.x * kRangePasses + p) * RPP + rl;
+    float m = 0.f;
+    if (r < sk) {
+#pragma unroll
+      for (int i = 0; i < 8; ++i) m = fmaxf(m, fabsf(__fsub_rn(x[p][i], mean[i])));
+    }
+#pragma unroll
+    for (int o = TPR / 2; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+    if (r < sk && cg == 0) keys[static_cast<long long>(bh) * sk + r] = __float_as_uint(m);
+  }
 }
 
 // ---------------------------------------------------------------------------------------
@@ -329,20 +339,26 @@ __global__ void __launch_bounds__(kThreads) quantize_qk_kernel(
     if (cg == 0) row_max[lr] = m;
   }
   __syncthreads();
-  if (threadIdx.x < kBlockRows) {
+  if (threadIdx.x < kBlockRows) {  // two full warps: lane = row & 31
     const int r = threadIdx.x;
-    float g = 0.f;
+    const float own = row_max[r], other = row_max[r ^ 32];
+    float g;
     if (!per_thread) {
-      const int lo = IS_KEY ? 0 : (r & ~31), n = IS_KEY ? 64 : 32;
-      for (int i = 0; i < n; ++i) g = fmaxf(g, row_max[lo + i]);
+      // one scale per 32 query rows (a warp) / per 64 key rows (both warps)
+      g = IS_KEY ? fmaxf(own, other) : own;
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) g = fmaxf(g, __shfl_xor_sync(0xffffffffu, g, o));
     } else if (!IS_KEY) {
       // rows {t, t+8, t+16, t+24} of each 32-row block (sage/reference.py:27-28)
-      const int lo = (r & ~31) + (r & 7);
-      for (int i = 0; i < 4; ++i) g = fmaxf(g, row_max[lo + 8 * i]);
+      g = fmaxf(own, __shfl_xor_sync(0xffffffffu, own, 8));
+      g = fmaxf(g, __shfl_xor_sync(0xffffffffu, g, 16));
     } else {
-      // rows 8a + 2t + c, a < 8, c < 2 (sage/reference.py:46-47)
-      const int t = (r & 7) >> 1;
-      for (int a = 0; a < 8; ++a) g = fmaxf(g, fmaxf(row_max[8 * a + 2 * t], row_max[8 * a + 2 * t + 1]));
+      // rows 8a + 2t + c, a < 8, c < 2 (sage/reference.py:46-47): every row that differs only in
+      // bit 0 (c) or bits 3-5 (a)
+      g = fmaxf(own, other);
+      g = fmaxf(g, __shfl_xor_sync(0xffffffffu, g, 1));
+      g = fmaxf(g, __shfl_xor_sync(0xffffffffu, g, 8));
+      g = fmaxf(g, __shfl_xor_sync(0xffffffffu, g, 16));
     }
     const float s = __fadd_rn(__fdiv_rn(g, 127.f), 1e-7f);
     row_scale[r] = s;
@@ -496,8 +512,8 @@ int run_prepass(const pk_problem& p, const Layout& L, Algo algo, cudaStream_t st
   // 2. key order
   const int32_t* order = nullptr;
   if (sort) {
-    constexpr int RPP = kThreads / (D / 8);
-    row_range_kernel<T, D, ALIGNED><<<dim3((L.Sk + RPP - 1) / RPP, BH), kThreads, 0, st>>>(
+    constexpr int RPB = kRangePasses * (kThreads / (D / 8));  // rows per CTA
+    row_range_kernel<T, D, ALIGNED><<<dim3((L.Sk + RPB - 1) / RPB, BH), kThreads, 0, st>>>(
         v, at<float>(p, L.v_mean), at<uint32_t>(p, L.range), L.Sk, p.heads);
     segment_sort_kernel<<<BH, kSortThreads, 0, st>>>(at<uint32_t>(p, L.range), at<uint32_t>(p, L.keys_alt),
                                                      at<int32_t>(p, L.idx_a), at<int32_t>(p, L.idx_b), L.Sk);

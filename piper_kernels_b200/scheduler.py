@@ -51,12 +51,42 @@ def gather_outputs(local: torch.Tensor, mine: range, flat_heads: int, shape, gro
     return full.reshape(shape)
 
 
+def plan_chunks(flat_heads: int, max_chunk: int) -> list[int]:
+    """Chunk sizes (in flat heads) for the host pipeline: they ramp up 1, 1, 2, 4 ... to
+    ``max_chunk`` and back down to 1, so that the first upload and the last download - the two
+    transfers nothing can hide - are one head long, while the bulk moves in large chunks whose
+    kernels fill whole waves of the GPU.  Every upload is at most twice the compute it hides behind."""
+    flat_heads, max_chunk = int(flat_heads), max(1, int(max_chunk))
+    ramp = [1]
+    while ramp[-1] * 2 < max_chunk:
+        ramp.append(ramp[-1] * 2)
+    front = [1] + ramp if max_chunk > 1 else []
+    back = ramp[::-1] if max_chunk > 1 else []
+    while front or back:  # too few heads for the full ramps: shorten them from the large end
+        if sum(front) + sum(back) <= flat_heads:
+            break
+        if len(back) >= len(front) - 1 and back:
+            back.pop(0)
+        else:
+            front.pop()
+    middle, rest = divmod(flat_heads - sum(front) - sum(back), max_chunk)
+    plan = front + [max_chunk] * middle + sorted(back + ([rest] if rest else []), reverse=True)
+    assert sum(plan) == flat_heads and all(0 < n <= max_chunk for n in plan)
+    return plan
+
+
 class HostAttentionPipeline:
     """Attention on inputs and outputs that live in pinned host memory.
 
-    Heads are independent, so the flat (batch x heads) axis is cut into chunks; the upload of
-    chunk i+1, the compute of chunk i and the download of chunk i-1 overlap on three CUDA
-    streams.  Device staging buffers (two slots per tensor) are allocated once and re-used.
+    Heads are independent, so the flat (batch x heads) axis is cut into chunks (see
+    :func:`plan_chunks`) and four CUDA streams overlap: the upload of chunk i+1, its quantisation
+    prepass (on a high-priority stream, so that its short kernels get SMs as soon as blocks of the
+    running fused kernel retire), the fused kernel of chunk i and the download of chunk i-1.
+    Device staging buffers (two slots per tensor) and the prepared calls (one per slot and chunk
+    size, each with its workspace and output) are allocated once and re-used.
+
+    ``op`` is the public function whose semantics are wanted, ``piper_attention`` or
+    ``sage_attention_2pp``; keyword arguments are the ones that function takes.
     """
 
     def __init__(self, device, *, heads_per_chunk: int = 8):
@@ -64,17 +94,48 @@ class HostAttentionPipeline:
         self.heads_per_chunk = int(heads_per_chunk)
         self.up = torch.cuda.Stream(self.device)
         self.down = torch.cuda.Stream(self.device)
+        self.prep = torch.cuda.Stream(self.device, priority=-1)
         self._slots = None
         self._key = None
+        self._calls = {}
 
     def _staging(self, q, k, v):
         key = (tuple(q.shape[2:]), tuple(k.shape[2:]), q.dtype)
         if self._key != key:
             n = self.heads_per_chunk
             mk = lambda t: torch.empty((n, *t.shape[2:]), dtype=t.dtype, device=self.device)  # noqa: E731
-            self._slots = [{"q": mk(q), "k": mk(k), "v": mk(v), "out": mk(q), "free": None, "drained": None} for _ in range(2)]
+            self._slots = [{"q": mk(q), "k": mk(k), "v": mk(v), "free": None} for _ in range(2)]
             self._key = key
+            self._calls = {}
         return self._slots
+
+    def _call(self, op, slot_index: int, n: int, kwargs: dict):
+        """Prepared call on the first ``n`` heads of a staging slot, with ``op``'s own defaults."""
+        from .attention._validation import validate_inputs
+        from .attention.piper import default_center_value, should_sort_value_rows
+        from .runtime import AttentionCall
+
+        name = getattr(op, "__name__", str(op))
+        if name not in ("piper_attention", "sage_attention_2pp"):
+            raise ValueError(f"HostAttentionPipeline runs piper_attention or sage_attention_2pp, not {name}")
+        key = (slot_index, n, name, tuple(sorted(kwargs.items())))
+        call = self._calls.get(key)
+        if call is None:
+            slot = self._slots[slot_index]
+            q, k, v = (slot[t][:n].unsqueeze(0) for t in ("q", "k", "v"))
+            causal = bool(kwargs.get("is_causal", False))
+            if name == "piper_attention":
+                scale = validate_inputs("Piper Attention", q, k, v, kwargs.get("scale"), causal)
+                center = kwargs.get("center_value")
+                center = default_center_value(q, k, causal) if center is None else bool(center)
+                sort = should_sort_value_rows(center_value=center, is_causal=causal, head_dim=q.shape[-1], key_length=k.shape[2])
+                call = AttentionCall("piper", q, k, v, scale, causal, center=center, sort=sort)
+            else:
+                scale = validate_inputs("SageAttention2++", q, k, v, kwargs.get("scale"), causal)
+                call = AttentionCall("sage2pp", q, k, v, scale, causal)
+            call.drained = None
+            self._calls[key] = call
+        return call
 
     def __call__(self, op, q_host, k_host, v_host, out_host, **kwargs) -> torch.Tensor:
         b, h = q_host.shape[:2]
@@ -83,34 +144,40 @@ class HostAttentionPipeline:
         fo = out_host.view(flat, *out_host.shape[2:])
         slots = self._staging(q_host, k_host, v_host)
         main = torch.cuda.current_stream(self.device)
-        self.up.wait_stream(main)
-        self.down.wait_stream(main)
-        for i, start in enumerate(range(0, flat, self.heads_per_chunk)):
-            n = min(flat, start + self.heads_per_chunk) - start
+        for s in (self.up, self.down, self.prep):
+            s.wait_stream(main)
+        start = 0
+        for i, n in enumerate(plan_chunks(flat, self.heads_per_chunk)):
             sl = slice(start, start + n)
+            start += n
             slot = slots[i % 2]
+            call = self._call(op, i % 2, n, kwargs)
             with torch.cuda.stream(self.up):
                 if slot["free"] is not None:
-                    self.up.wait_event(slot["free"])  # the compute that read this slot has finished
+                    self.up.wait_event(slot["free"])  # the fused kernel that read this slot has finished
                 slot["q"][:n].copy_(fq[sl], non_blocking=True)
                 slot["k"][:n].copy_(fk[sl], non_blocking=True)
                 slot["v"][:n].copy_(fv[sl], non_blocking=True)
                 uploaded = torch.cuda.Event()
                 uploaded.record(self.up)
-            main.wait_event(uploaded)
-            if slot["drained"] is not None:
-                main.wait_event(slot["drained"])  # the download of this slot's previous result has finished
-            out = op(slot["q"][:n].unsqueeze(0), slot["k"][:n].unsqueeze(0), slot["v"][:n].unsqueeze(0), **kwargs)
-            slot["out"][:n].copy_(out[0])
+            with torch.cuda.stream(self.prep):
+                self.prep.wait_event(uploaded)
+                call.prepare()
+                prepared = torch.cuda.Event()
+                prepared.record(self.prep)
+            main.wait_event(prepared)
+            if call.drained is not None:
+                main.wait_event(call.drained)  # the download of this call's previous result has finished
+            call.run()
             slot["free"] = torch.cuda.Event()
             slot["free"].record(main)
             with torch.cuda.stream(self.down):
                 self.down.wait_event(slot["free"])
-                fo[sl].copy_(slot["out"][:n], non_blocking=True)
-                slot["drained"] = torch.cuda.Event()
-                slot["drained"].record(self.down)
-        main.wait_stream(self.down)
-        main.wait_stream(self.up)
+                fo[sl].copy_(call.out[0], non_blocking=True)
+                call.drained = torch.cuda.Event()
+                call.drained.record(self.down)
+        for s in (self.down, self.up, self.prep):
+            main.wait_stream(s)
         return out_host
 
 

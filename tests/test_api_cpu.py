@@ -143,3 +143,17 @@ def test_fake_kernel_shapes():
     assert out.shape == q.shape and out.is_contiguous() and out.dtype == q.dtype
     out = _ops.sage_attention_2pp_op(q, q, q, 0.125, False)
     assert out.shape == q.shape and out.is_contiguous()
+
+
+def test_host_pipeline_chunk_plan_covers_every_head_and_ramps():
+    from piper_kernels_b200.scheduler import plan_chunks
+
+    for flat in range(1, 70):
+        for max_chunk in (1, 2, 3, 4, 8, 16):
+            plan = plan_chunks(flat, max_chunk)
+            assert sum(plan) == flat
+            assert all(1 <= n <= max_chunk for n in plan)
+            assert plan[0] == 1 and plan[-1] == 1  # the exposed first upload / last download are one head
+            # an upload never exceeds twice the chunk whose compute hides it
+            assert all(b <= 2 * a for a, b in zip(plan, plan[1:]))
+    assert plan_chunks(40, 8) == [1, 1, 2, 4, 8, 8, 8, 4, 2, 1, 1]
