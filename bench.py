@@ -265,7 +265,7 @@ def ours_arm(args, w, rank, local_rank, world):
     del call
 
     # end to end from pinned host memory through the public host entry point: per-head-chunk upload,
-    # compute and download overlap on three streams (heads are independent)
+    # prepass, fused kernel and download overlap on four streams (heads are independent)
     e2e = None
     if not args.no_e2e:
         from piper_kernels_b200.scheduler import HostAttentionPipeline
@@ -279,7 +279,7 @@ def ours_arm(args, w, rank, local_rank, world):
         hout = torch.empty(q.shape, dtype=q.dtype).pin_memory()
         kwargs = dict(is_causal=w.causal, center_value=w.center) if w.op == "piper" else dict(is_causal=w.causal)
         fn = pk.piper_attention if w.op == "piper" else pk.sage_attention_2pp
-        chunk = max(1, min(8, w.flat_heads // 4))
+        chunk = max(1, min(4, w.flat_heads // 4))
         pipe = HostAttentionPipeline(dev, heads_per_chunk=chunk)
 
         def e2e_step():
@@ -291,7 +291,7 @@ def ours_arm(args, w, rank, local_rank, world):
         h2d = sum(t.numel() * t.element_size() for t in (hq, hk, hv))
         e2e = {"value": world * ops_per_gpu / (e2e_ms * 1e-3) / 1e12, "unit": UNIT, "ms_per_step": e2e_ms,
                "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": hout.numel() * hout.element_size(),
-               "api": f"scheduler.HostAttentionPipeline, {chunk} heads per chunk, pinned host buffers"}
+               "api": f"scheduler.HostAttentionPipeline, ramped chunks of up to {chunk} heads, pinned host buffers"}
 
     if rank != 0:
         if dist is not None:

@@ -89,7 +89,7 @@ class HostAttentionPipeline:
     ``sage_attention_2pp``; keyword arguments are the ones that function takes.
     """
 
-    def __init__(self, device, *, heads_per_chunk: int = 8):
+    def __init__(self, device, *, heads_per_chunk: int = 4):
         self.device = torch.device(device)
         self.heads_per_chunk = int(heads_per_chunk)
         self.up = torch.cuda.Stream(self.device)
@@ -182,6 +182,6 @@ class HostAttentionPipeline:
 
 
 def attention_from_host(op, q_host: torch.Tensor, k_host: torch.Tensor, v_host: torch.Tensor,
-                        out_host: torch.Tensor, device, *, heads_per_chunk: int = 8, **kwargs) -> torch.Tensor:
+                        out_host: torch.Tensor, device, *, heads_per_chunk: int = 4, **kwargs) -> torch.Tensor:
     """One-shot form of :class:`HostAttentionPipeline` (allocates the staging buffers per call)."""
     return HostAttentionPipeline(device, heads_per_chunk=heads_per_chunk)(op, q_host, k_host, v_host, out_host, **kwargs)
