@@ -54,6 +54,9 @@
 #ifndef PK_NSWG_PIPER
 #define PK_NSWG_PIPER 2
 #endif
+#ifndef PK_NSWG_SAGE
+#define PK_NSWG_SAGE 2
+#endif
 // per-role register allocations (piper): softmax, dequant, helper warpgroups
 #ifndef PK_REG_SM
 #define PK_REG_SM 112
@@ -68,7 +71,8 @@ constexpr int NK = 8;      // K tile ring
 constexpr int NV = 4;      // V^T tile ring
 constexpr int NVEC = 16;   // per-key vector ring (k_mul, k_add, k_inv: 3 x 64 floats)
 constexpr int NSTAT = 8;   // softmax -> dequant per-row statistics ring
-// sage runs 384 threads (168 registers each at launch): softmax / dequant 232 / helpers 48
+constexpr int NM = 4;      // sage: running-maximum hand-over ring between the two softmax warpgroups
+// sage with one softmax warpgroup runs 384 threads (168 registers each at launch): softmax / dequant 232 / helpers 48
 #ifndef PK_REG_SM_SAGE
 #define PK_REG_SM_SAGE 152
 #endif
@@ -103,10 +107,17 @@ struct FusedParams {
 
 template <int D, int ALGO>
 struct Cfg {
-  static constexpr int NSWG = (ALGO == kPiper) ? PK_NSWG_PIPER : 1;
+  static constexpr int NSWG = (ALGO == kPiper) ? PK_NSWG_PIPER : PK_NSWG_SAGE;
   static constexpr int NDQ = PK_NDQ;  // dequant warpgroups; each folds D / NDQ columns of every partial
   static constexpr int THREADS = (NSWG + NDQ + 1) * 128;
   static constexpr int LAUNCH_REGS = (65536 / THREADS) / 8 * 8;  // registers per thread at launch
+  // Per-role register budgets (setmaxnreg).  512 threads start with 128 registers each, 384 with
+  // 168; the budgets of all warpgroups must fit the 64 K registers of the SM.
+  static constexpr bool FOUR_WG = THREADS == 512;
+  static constexpr int REG_SM = (ALGO == kPiper) ? PK_REG_SM : (FOUR_WG ? (D == 64 ? 152 : 112) : PK_REG_SM_SAGE);
+  static constexpr int REG_DQ = (ALGO == kPiper) ? PK_REG_DQ : (FOUR_WG ? (D == 64 ? 144 : 232) : 232);
+  static constexpr int REG_HELPER = (ALGO == kPiper) ? PK_REG_HELPER : (FOUR_WG ? 56 : 48);
+  static_assert((NSWG * REG_SM + NDQ * REG_DQ + REG_HELPER) * 128 <= 65536, "register budgets exceed the SM");
   static constexpr int Q_BYTES = kQTile * D;
   static constexpr int K_BYTES = kKeyTile * D;
   static constexpr int V_BYTES = D * kKeyTile;
@@ -115,8 +126,9 @@ struct Cfg {
   static constexpr int OFF_V = OFF_K + NK * K_BYTES;
   static constexpr int OFF_VEC = OFF_V + NV * V_BYTES;
   static constexpr int OFF_STAT = OFF_VEC + NVEC * VEC_FLOATS * 4;
-  static constexpr int OFF_BAR = OFF_STAT + NSTAT * kQTile * 8;
-  static constexpr int NUM_BARS = 1 + 2 * NK + NV + NVEC + NS + 2 * NP + NO + NSTAT;
+  static constexpr int OFF_MRING = OFF_STAT + NSTAT * kQTile * 8;
+  static constexpr int OFF_BAR = OFF_MRING + NM * kQTile * 4;
+  static constexpr int NUM_BARS = 1 + 2 * NK + NV + NVEC + NS + 2 * NP + NO + NSTAT + NM;
   static constexpr int OFF_MISC = (OFF_BAR + NUM_BARS * 8 + 15) / 16 * 16;
   static constexpr int OFF_MAGIC = OFF_MISC + 16;           // 16 words holding the arming pattern
   static constexpr int SMEM_BYTES = OFF_MAGIC + 64 + 1024;  // + slack for 1024-byte alignment
@@ -144,13 +156,14 @@ struct Bars {
   __device__ uint32_t pv_done(int i) const { return at(1 + 2 * NK + NV + NVEC + NS + NP + i); }
   __device__ uint32_t o_empty(int i) const { return at(1 + 2 * NK + NV + NVEC + NS + 2 * NP + i); }
   __device__ uint32_t stat_full(int i) const { return at(1 + 2 * NK + NV + NVEC + NS + 2 * NP + NO + i); }
+  __device__ uint32_t m_ready(int i) const { return at(1 + 2 * NK + NV + NVEC + NS + 2 * NP + NO + NSTAT + i); }
 };
 static_assert(NV == NP, "pv_done serves the V ring and the probability ring with one index");
 
 // wait-site codes reported in status[0] when a wait is abandoned
 enum : int {
   W_PROD_K = 11, W_PROD_V = 12, W_QK_Q = 21, W_QK_K = 22, W_QK_S = 23, W_PV_P = 26, W_PV_O = 27, W_PV_V = 28,
-  W_SM_VEC = 31, W_SM_S = 32, W_SM_PV = 33, W_DQ_STAT = 41, W_DQ_O = 42
+  W_SM_VEC = 31, W_SM_S = 32, W_SM_PV = 33, W_SM_M = 34, W_DQ_STAT = 41, W_DQ_O = 42
 };
 
 // Per-role timeline of one CTA for pk_debug_timeline(): int64 clock64() stamps laid out
@@ -207,6 +220,7 @@ fused_attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
   volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + C::OFF_MISC + 4);
   float* vec_ring = reinterpret_cast<float*>(smem + C::OFF_VEC);
   float2* stat_ring = reinterpret_cast<float2*>(smem + C::OFF_STAT);
+  float* m_ring = reinterpret_cast<float*>(smem + C::OFF_MRING);
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, wg = warp >> 2;
   const int bh = blockIdx.y;
@@ -229,6 +243,7 @@ fused_attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
     for (int i = 0; i < NP; ++i) { mbar_init(bars.p_ready(i), 128); mbar_init(bars.pv_done(i), 1); }
     for (int i = 0; i < NO; ++i) mbar_init(bars.o_empty(i), 128 * C::NDQ);
     for (int i = 0; i < NSTAT; ++i) mbar_init(bars.stat_full(i), 128);
+    for (int i = 0; i < NM; ++i) mbar_init(bars.m_ready(i), 128);
     *abort_flag = 0;
     fence_barrier_init();
   }
@@ -248,7 +263,7 @@ fused_attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
   // The CTA starts with 128 (piper, 512 threads) or 168 (sage, 384 threads) registers per
   // thread; the dequant rows need more and the helper warpgroup far fewer, so each role
   // resizes its allocation on entry.
-  if (wg == NSWG + C::NDQ) setmaxnreg_dec<(ALGO == kPiper ? PK_REG_HELPER : 48)>();
+  if (wg == NSWG + C::NDQ) setmaxnreg_dec<C::REG_HELPER>();
 
   if (warp == PROD_WARP) {
     // ------------------------------------------------------------------ producer
@@ -339,7 +354,7 @@ fused_attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
     }
   } else if (wg < NSWG) {
     // ------------------------------------------------------------------ softmax
-    if (ALGO == kPiper) { if (PK_REG_SM <= C::LAUNCH_REGS) setmaxnreg_dec<PK_REG_SM>(); else setmaxnreg_inc<PK_REG_SM>(); } else setmaxnreg_dec<PK_REG_SM_SAGE>();
+    if (C::REG_SM <= C::LAUNCH_REGS) setmaxnreg_dec<C::REG_SM>(); else setmaxnreg_inc<C::REG_SM>();
     const int row = tid & 127;
     const uint32_t lane_addr = tmem_base + (static_cast<uint32_t>((warp & 3) * 32) << 16);
     const float qm = prm.q_mul[static_cast<long long>(bh) * prm.sq_pad + q0 + row];
@@ -426,7 +441,19 @@ fused_attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
       if (ALGO == kPiper) {
         shift = (bm == -INFINITY) ? 0.f : -bm;
       } else {
+        // Sage's codes are relative to the running maximum.  With two softmax warpgroups on
+        // alternate tiles the maximum after tile j-1 comes from the other warpgroup through shared
+        // memory; only this short hand-over is sequential, the exponentials of consecutive tiles
+        // overlap.
+        if (NSWG > 1 && j > 0) {
+          if (!WARP_ALL(mbar_wait_bounded(bars.m_ready((j - 1) % NM), ((j - 1) / NM) & 1, abort_flag, W_SM_M))) break;
+          m_run = m_ring[((j - 1) % NM) * kQTile + row];
+        }
         const float nm = fmaxf(m_run, bm);
+        if (NSWG > 1) {
+          m_ring[(j % NM) * kQTile + row] = nm;
+          mbar_arrive(bars.m_ready(j % NM));
+        }
         const float ns = (nm == -INFINITY) ? 0.f : nm;
         ow = (m_run == nm) ? 1.f : ex2_approx(m_run - ns);
         shift = 8.807354922057604f - ns;  // log2(448): P = e4m3(448 * 2^(t - max))
@@ -483,7 +510,7 @@ fused_attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
     }
   } else if (wg < NSWG + C::NDQ) {
     // ------------------------------------------------------------------ dequant + epilogue
-    if (ALGO == kPiper) setmaxnreg_inc<PK_REG_DQ>(); else setmaxnreg_inc<(C::NDQ == 1 ? 232 : 136)>();
+    setmaxnreg_inc<C::REG_DQ>();
     constexpr int DH = D / C::NDQ;          // columns folded by this warpgroup
     constexpr int CH = (DH % PK_DQ_CHUNK == 0) ? PK_DQ_CHUNK : 16;  // columns per tensor-memory round trip
     const int col0 = (wg - NSWG) * DH;      // first of them
