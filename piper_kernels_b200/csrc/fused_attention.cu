@@ -17,8 +17,10 @@
 //   producer warp         TMA loads of the Q tile, K tiles, V^T tiles and per-key vectors
 //   two issue warps       one thread each issues tcgen05.mma: S = Q K^T (SS form, kind::i8) and
 //                         O_part = P V (A from tensor memory; kind::i8 U8xS8 or kind::f8f6f4)
-// Piper's probability codes depend only on the tile's own maximum, so two softmax warpgroups
-// process alternate key tiles in parallel; Sage's depend on the running maximum, so it uses one.
+// Two softmax warpgroups process alternate key tiles.  Piper's probability codes depend only on
+// the tile's own maximum; Sage's depend on the running maximum, which one warpgroup hands to the
+// other through shared memory as soon as it knows its tile's maximum, so that only this short
+// step is sequential and the exponentials of consecutive tiles overlap.
 //
 // INT32 accumulators are read as FP32 without an integer instruction: every INT32 buffer is
 // re-armed with the bit pattern of 1.5*2^23 by the warp that has just read it, and the next
@@ -285,11 +287,12 @@ fused_attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
           // release waited for above (NVEC >= NK + NS + 2).
           const int vs = i % NVEC;
           const uint32_t vdst = smem_base + C::OFF_VEC + vs * VEC_FLOATS * 4;
-          mbar_expect_tx(bars.vec_full(vs), VEC_FLOATS * 4);
+          const uint32_t vbar = bars.vec_full(vs);
+          mbar_expect_tx(vbar, VEC_FLOATS * 4);
           const long long off = vec_base + static_cast<long long>(i) * kKeyTile;
-          bulk_load(vdst, prm.k_mul + off, kKeyTile * 4, bars.vec_full(vs));
-          bulk_load(vdst + kKeyTile * 4, prm.k_add + off, kKeyTile * 4, bars.vec_full(vs));
-          bulk_load(vdst + 2 * kKeyTile * 4, prm.k_inv + off, kKeyTile * 4, bars.vec_full(vs));
+          bulk_load(vdst, prm.k_mul + off, kKeyTile * 4, vbar);
+          bulk_load(vdst + kKeyTile * 4, prm.k_add + off, kKeyTile * 4, vbar);
+          bulk_load(vdst + 2 * kKeyTile * 4, prm.k_inv + off, kKeyTile * 4, vbar);
           }
         }
         const int j = i - V_LAG;
