@@ -33,10 +33,10 @@ METRIC = "attention_tops"
 UNIT = "TOPS"
 NOMINAL_INT8_TOPS = 4500.0
 # DRAM bytes per launch of the fused kernel per query row (read + write), from the ncu capture of
-# workload c2 summarised in profiles/fused_attention_kernel_c2_ncu_full.md: 98.4 MB for 48 heads
+# workload c2 summarised in profiles/fused_attention_kernel_c2_ncu_full.md: 99.3 MB for 48 heads
 # x 4096 rows at D=128.  Traffic grows with batch*heads*rows (K/V of a head stay in L2 while its
 # query tiles run), so other D=128 workloads scale by their row count.
-FUSED_DRAM_BYTES_PER_ROW_D128 = 98.4e6 / (48 * 4096)
+FUSED_DRAM_BYTES_PER_ROW_D128 = 99.3e6 / (48 * 4096)
 
 
 def parse_args():
