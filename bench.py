@@ -39,6 +39,9 @@ NOMINAL_INT8_TOPS = 4500.0
 FUSED_DRAM_BYTES_PER_ROW_D128 = 99.3e6 / (48 * 4096)
 
 
+_JSON_OUT = None  # duplicate of the original standard output, set in main()
+
+
 def parse_args():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -137,7 +140,7 @@ def reference_arm(args, w, rank, world):
         "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }
-    print(json.dumps(line), flush=True)
+    print(json.dumps(line), file=_JSON_OUT or sys.stdout, flush=True)
 
 
 # --------------------------------------------------------------------------------------
@@ -217,8 +220,6 @@ def ours_arm(args, w, rank, local_rank, world):
     dist = None
     if world > 1:
         import torch.distributed as dist
-        if os.environ.get("NCCL_DEBUG", "").upper() not in ("INFO", "TRACE"):
-            os.environ["NCCL_DEBUG"] = "WARN"  # keep NCCL's version banner off stdout (one JSON line only)
         dist.init_process_group("nccl", device_id=dev)
 
     def barrier():
@@ -329,7 +330,7 @@ def ours_arm(args, w, rank, local_rank, world):
         "gpu_launches": (prepass_launches + 1) * args.steps, "roofline": roofline, "cpu_baseline": cpu_baseline,
         "device_status": status[0],
     }
-    print(json.dumps(line), flush=True)
+    print(json.dumps(line), file=_JSON_OUT or sys.stdout, flush=True)
     if dist is not None:
         dist.destroy_process_group()
 
@@ -346,6 +347,15 @@ def main():
                str(Path(__file__).resolve()), *sys.argv[1:]]
         raise SystemExit(subprocess.call(cmd))
     from piper_kernels_b200.workloads import WORKLOADS
+
+    # Standard output carries exactly one JSON line.  Libraries loaded below write banners to
+    # file descriptor 1 from C code (NCCL prints its version there), so descriptor 1 is pointed at
+    # standard error for the run and the JSON line goes to a duplicate of the original.
+    sys.stdout.flush()
+    json_out = os.fdopen(os.dup(1), "w")
+    os.dup2(2, 1)
+    global _JSON_OUT
+    _JSON_OUT = json_out
 
     w = WORKLOADS[args.workload]
     if args.impl == "reference":
