@@ -124,8 +124,8 @@ PK_API int pk_debug_first_tile(const pk_problem* p, int sage, int bh, int q_tile
 
 /* Profiling aid: runs the ordinary fused kernel and records, for the CTA of query tile `q_tile`
  * of flattened head `bh`, clock64() stamps of every warp role per key tile into `stamps`
- * (device memory, int64 [6 roles][max_tiles][8]; roles: 0/1 softmax warpgroups, 2 dequant,
- * 3 S-product issue, 4 PV-product issue, 5 producer). */
+ * (device memory, int64 [7 roles][max_tiles][8]; roles: the softmax warpgroups first - two at
+ * head_dim 128, three at head_dim 64 - then dequant, S-product issue, PV-product issue). */
 PK_API int pk_debug_timeline(const pk_problem* p, int sage, int bh, int q_tile, void* stamps, int max_tiles);
 
 /* K and V sequence means ([batch*heads, head_dim] f32 each, device memory) computed without a

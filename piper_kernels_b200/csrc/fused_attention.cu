@@ -59,6 +59,11 @@
 #ifndef PK_NSWG_SAGE
 #define PK_NSWG_SAGE 2
 #endif
+// softmax warpgroups at head_dim 64 (a third one would have to run in 96 registers: the CTA owns
+// only the registers it was launched with, 640 x 96)
+#ifndef PK_NSWG_D64
+#define PK_NSWG_D64 2
+#endif
 // per-role register allocations (piper): softmax, dequant, helper warpgroups
 #ifndef PK_REG_SM
 #define PK_REG_SM 112
@@ -109,17 +114,21 @@ struct FusedParams {
 
 template <int D, int ALGO>
 struct Cfg {
-  static constexpr int NSWG = (ALGO == kPiper) ? PK_NSWG_PIPER : PK_NSWG_SAGE;
+  static constexpr int NSWG = (D == 64) ? PK_NSWG_D64 : ((ALGO == kPiper) ? PK_NSWG_PIPER : PK_NSWG_SAGE);
   static constexpr int NDQ = PK_NDQ;  // dequant warpgroups; each folds D / NDQ columns of every partial
   static constexpr int THREADS = (NSWG + NDQ + 1) * 128;
   static constexpr int LAUNCH_REGS = (65536 / THREADS) / 8 * 8;  // registers per thread at launch
   // Per-role register budgets (setmaxnreg).  512 threads start with 128 registers each, 384 with
   // 168; the budgets of all warpgroups must fit the 64 K registers of the SM.
-  static constexpr bool FOUR_WG = THREADS == 512;
-  static constexpr int REG_SM = (ALGO == kPiper) ? PK_REG_SM : (FOUR_WG ? (D == 64 ? 152 : 112) : PK_REG_SM_SAGE);
-  static constexpr int REG_DQ = (ALGO == kPiper) ? PK_REG_DQ : (FOUR_WG ? (D == 64 ? 144 : 232) : 232);
-  static constexpr int REG_HELPER = (ALGO == kPiper) ? PK_REG_HELPER : (FOUR_WG ? 56 : 48);
-  static_assert((NSWG * REG_SM + NDQ * REG_DQ + REG_HELPER) * 128 <= 65536, "register budgets exceed the SM");
+  static constexpr bool FOUR_WG = THREADS == 512, FIVE_WG = THREADS == 640;
+  static constexpr int REG_SM = FIVE_WG ? 96 : (ALGO == kPiper) ? PK_REG_SM : (FOUR_WG ? (D == 64 ? 152 : 112) : PK_REG_SM_SAGE);
+  static constexpr int REG_DQ = FIVE_WG ? 136 : (ALGO == kPiper) ? PK_REG_DQ : (FOUR_WG ? (D == 64 ? 144 : 232) : 232);
+  static constexpr int REG_HELPER = FIVE_WG ? 40 : (ALGO == kPiper) ? PK_REG_HELPER : (FOUR_WG ? 56 : 48);
+  static_assert(!FIVE_WG || D == 64, "five warpgroups leave the dequant rows 136 registers: head_dim 64 only");
+  // setmaxnreg only moves registers between the warps of the CTA: an increase waits (without a time
+  // limit) until other warps have released enough, so the budgets must fit what the CTA was launched with.
+  static_assert((NSWG * REG_SM + NDQ * REG_DQ + REG_HELPER) * 128 <= THREADS * LAUNCH_REGS,
+                "role register budgets exceed the registers the CTA owns");
   static constexpr int Q_BYTES = kQTile * D;
   static constexpr int K_BYTES = kKeyTile * D;
   static constexpr int V_BYTES = D * kKeyTile;
@@ -169,9 +178,9 @@ enum : int {
 };
 
 // Per-role timeline of one CTA for pk_debug_timeline(): int64 clock64() stamps laid out
-// [role][tile][8], roles: 0/1 softmax warpgroups, 2 dequant, 3 S-product issue, 4 PV-product
-// issue, 5 producer.  One thread per role stamps; other CTAs and ordinary launches skip it.
-constexpr int kTimelineRoles = 6;
+// [role][tile][8], roles: the softmax warpgroups first (two at head_dim 128, three at 64), then
+// dequant, S-product issue, PV-product issue; at most 7 roles.  One thread per role stamps; other
+// CTAs and ordinary launches skip it.
 #define PK_STAMP(role, tile, k)                                                                     \
   do {                                                                                               \
     if (TIMELINE && stamping && (tile) < prm.timeline_tiles)                                         \
@@ -317,17 +326,17 @@ fused_attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
       const uint64_t kdesc0 = umma_smem_desc(smem_base + C::OFF_K, D);
       bool ok = mbar_wait_bounded(bars.q_full(), 0, abort_flag, W_QK_Q);
       for (int j = 0; ok && j < n_tiles; ++j) {
-        PK_STAMP(3, j, 0);
+        PK_STAMP(NSWG + 1, j, 0);
         if (!mbar_wait_bounded(bars.k_full(j % NK), (j / NK) & 1, abort_flag, W_QK_K)) break;
         if (!mbar_wait_bounded(bars.s_free(j % NS), (j / NS) & 1, abort_flag, W_QK_S)) break;
         tc_fence_after();
-        PK_STAMP(3, j, 1);
+        PK_STAMP(NSWG + 1, j, 1);
         const uint64_t kdesc = kdesc0 + static_cast<uint64_t>(((j % NK) * C::K_BYTES) >> 4);
         const uint32_t d = tmem_base + C::COL_S + (j % NS) * kKeyTile;
 #pragma unroll
         for (int kk = 0; kk < D / 32; ++kk) umma_i8_ss(d, qdesc + 2 * kk, kdesc + 2 * kk, idesc_qk, 1u);
         tc_commit(bars.qk_done(j % NK));
-        PK_STAMP(3, j, 2);
+        PK_STAMP(NSWG + 1, j, 2);
       }
     }
   } else if (warp == PV_WARP) {
@@ -337,12 +346,12 @@ fused_attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
                                                      : umma_idesc(kAccF32, kFmtE4M3, kFmtE4M3, kQTile, D);
       const uint64_t vdesc0 = umma_smem_desc(smem_base + C::OFF_V, kKeyTile);
       for (int j = 0; j < n_tiles; ++j) {
-        PK_STAMP(4, j, 0);
+        PK_STAMP(NSWG + 2, j, 0);
         if (!mbar_wait_bounded(bars.p_ready(j % NP), (j / NP) & 1, abort_flag, W_PV_P)) break;
         if (!mbar_wait_bounded(bars.o_empty(j % NO), (j / NO) & 1, abort_flag, W_PV_O)) break;
         if (!mbar_wait_bounded(bars.v_full(j % NV), (j / NV) & 1, abort_flag, W_PV_V)) break;
         tc_fence_after();
-        PK_STAMP(4, j, 1);
+        PK_STAMP(NSWG + 2, j, 1);
         const uint64_t vdesc = vdesc0 + static_cast<uint64_t>(((j % NV) * C::V_BYTES) >> 4);
         const uint32_t d = tmem_base + C::COL_O + (j % NO) * D;
         const uint32_t a = tmem_base + C::COL_P + (j % NP) * (kKeyTile / 4);
@@ -352,7 +361,7 @@ fused_attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
           else umma_f8_ts(d, a + 8 * kk, vdesc + 2 * kk, idesc_pv, kk > 0);
         }
         tc_commit(bars.pv_done(j % NP));
-        PK_STAMP(4, j, 2);
+        PK_STAMP(NSWG + 2, j, 2);
       }
     }
   } else if (wg < NSWG) {
@@ -578,7 +587,7 @@ fused_attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
       }
     }
     for (int j = 0; ok && j < n_tiles; ++j) {
-      PK_STAMP(2, j, 0);
+      PK_STAMP(NSWG, j, 0);
       ow = ow_n; c = c_n;
       const uint32_t o_addr = lane_addr + C::COL_O + (j % NO) * D + col0;
       if (WARP_ANY(ow != 1.f)) {
@@ -587,11 +596,11 @@ fused_attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
         for (int d = 0; d < DH / 2; ++d) num2[d] = __fmul2_rn(num2[d], ow2);
       }
       const float2 c2 = make_float2(c, c);
-      PK_STAMP(2, j, 1);
+      PK_STAMP(NSWG, j, 1);
 #pragma unroll
       for (int ch = 0; ch < NCH; ++ch) {
         tmem_wait_ld();
-        if (ch == 0) PK_STAMP(2, j, 2);
+        if (ch == 0) PK_STAMP(NSWG, j, 2);
         if (ch + 1 < NCH) {
           tmem_ldN<CH>(o_addr + (ch + 1) * CH, obuf[(ch + 1) & 1]);
         } else if (j + 1 < n_tiles && ok) {
@@ -599,12 +608,12 @@ fused_attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
           tmem_ldN<CH>(lane_addr + C::COL_O + ((j + 1) % NO) * D + col0, obuf[(ch + 1) & 1]);
         }
         if (ch == STAT_AT && j + 1 < n_tiles) {
-          PK_STAMP(2, j, 4);
+          PK_STAMP(NSWG, j, 4);
           ok = advance_stats(j + 1);
-          PK_STAMP(2, j, 7);
+          PK_STAMP(NSWG, j, 7);
           ok = ok && WARP_ALL(mbar_wait_bounded(bars.pv_done((j + 1) % NP), ((j + 1) / NP) & 1, abort_flag, W_DQ_O));
           tc_fence_after();
-          PK_STAMP(2, j, 5);
+          PK_STAMP(NSWG, j, 5);
         }
         if (O_MAGIC) {
 #pragma unroll
@@ -627,11 +636,11 @@ fused_attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
           }
         }
       }
-      PK_STAMP(2, j, 6);
+      PK_STAMP(NSWG, j, 6);
       if (O_MAGIC) tmem_wait_st();
       tc_fence_before();
       mbar_arrive(bars.o_empty(j % NO));
-      PK_STAMP(2, j, 3);
+      PK_STAMP(NSWG, j, 3);
     }
     // epilogue: normalise, restore the V mean (piper) / apply the channel scale (sage), cast
     const int grow = q0 + row;

@@ -19,7 +19,7 @@ from .attention.piper import default_center_value, should_sort_value_rows
 from .runtime import AttentionCall
 from .workloads import WORKLOADS, make_inputs
 
-ROLES = 6
+ROLES = 7
 
 
 def capture(call: AttentionCall, bh: int, q_tile: int, max_tiles: int = 1024) -> np.ndarray:
@@ -42,7 +42,7 @@ def summarize(tr: np.ndarray, n_tiles: int, nswg: int) -> str:
     tr = np.where(tr > 0, tr - t0, -1)[:, :n]
     lo, hi = min(8, n // 4), n - 2
     d = lambda x, a, b: float(np.mean(x[:, b] - x[:, a]))  # noqa: E731
-    lines = [f"tiles {n}; total {int(tr.max())} cycles; steady-state period {(tr[2, hi, 3] - tr[2, lo, 3]) / (hi - lo):.0f} cycles per tile"]
+    lines = [f"tiles {n}; total {int(tr.max())} cycles; steady-state period {(tr[nswg, hi, 3] - tr[nswg, lo, 3]) / (hi - lo):.0f} cycles per tile"]
     for w in range(nswg):
         x = tr[w, lo + ((w - lo) % nswg):hi:nswg]
         if x[:, 4].min() >= 0:  # single-pass softmax stamps
@@ -51,17 +51,17 @@ def summarize(tr: np.ndarray, n_tiles: int, nswg: int) -> str:
                          f"per own tile {np.mean(np.diff(x[:, 0])):.0f}")
         else:
             lines.append(f"softmax{w}: wait {d(x, 0, 1):.0f} | pass 1 {d(x, 1, 2):.0f} | pass 2 + publish {d(x, 2, 3):.0f} | per own tile {np.mean(np.diff(x[:, 0])):.0f}")
-    x = tr[2, lo:hi]
+    x = tr[nswg, lo:hi]
     lines.append(f"dequant : rescale {d(x, 0, 1):.0f} | first chunk {d(x, 1, 2):.0f} | early chunks {d(x, 2, 4):.0f} | "
                  f"next tile's statistics {d(x, 4, 7):.0f} | next tile's product wait {d(x, 7, 5):.0f} | remaining chunks {d(x, 5, 6):.0f} | "
                  f"release {d(x, 6, 3):.0f} | per tile {np.mean(np.diff(x[:, 0])):.0f}")
-    for r, name in ((3, "S issue "), (4, "PV issue")):
+    for r, name in ((nswg + 1, "S issue "), (nswg + 2, "PV issue")):
         x = tr[r, lo:hi]
         lines.append(f"{name}: wait {d(x, 0, 1):.0f} | issue {d(x, 1, 2):.0f} | per tile {np.mean(np.diff(x[:, 0])):.0f}")
     own = np.arange(n) % nswg
     p_done = tr[own, np.arange(n), 3]
-    lines.append(f"P published -> PV issued {np.mean(tr[4, lo:hi, 2] - p_done[lo:hi]):.0f} | PV issued -> fold begins {np.mean(tr[2, lo:hi, 0] - tr[4, lo:hi, 2]):.0f} | "
-                 f"S issued -> softmax picks it up {np.mean(tr[own, np.arange(n), 1][lo:hi] - tr[3, lo:hi, 2]):.0f}")
+    lines.append(f"P published -> PV issued {np.mean(tr[nswg + 2, lo:hi, 2] - p_done[lo:hi]):.0f} | PV issued -> fold begins {np.mean(tr[nswg, lo:hi, 0] - tr[nswg + 2, lo:hi, 2]):.0f} | "
+                 f"S issued -> softmax picks it up {np.mean(tr[own, np.arange(n), 1][lo:hi] - tr[nswg + 1, lo:hi, 2]):.0f}")
     return "\n".join(lines)
 
 
@@ -88,7 +88,7 @@ def main() -> None:
     n_tiles = (w.kv_len + 63) // 64
     if w.causal:
         n_tiles = min(n_tiles, 2 * a.q_tile + 2)
-    print(summarize(tr, n_tiles, 2))
+    print(summarize(tr, n_tiles, 3 if w.head_dim == 64 else 2))
     if a.save:
         np.save(a.save, tr)
 
