@@ -88,7 +88,7 @@ def main() -> None:
     n_tiles = (w.kv_len + 63) // 64
     if w.causal:
         n_tiles = min(n_tiles, 2 * a.q_tile + 2)
-    print(summarize(tr, n_tiles, 3 if w.head_dim == 64 else 2))
+    print(summarize(tr, n_tiles, 2))
     if a.save:
         np.save(a.save, tr)
 
