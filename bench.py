@@ -316,6 +316,22 @@ def ours_arm(args, w, rank, local_rank, world):
         "peak_note": peak_note,
         "frac_of_nominal_int8": achieved / NOMINAL_INT8_TOPS, "ms_per_launch": fused_ms, "prepass_ms": prep_ms,
     }
+    # The prepass is byte work bound by HBM: 2 bytes read + 1 byte written per input element of
+    # q, k and v (the second read of K/V for "statistics, then quantise" should hit L2), plus the
+    # per-key vectors; the whole prepass (all its launches) is timed as one unit.
+    hbm_peak = peaks.get("hbm_gbs")
+    prepass_bytes = 3 * w.flat_heads * (w.q_len + 2 * w.kv_len) * w.head_dim + 16 * w.flat_heads * w.kv_len
+    prepass_gbs = prepass_bytes / (prep_ms * 1e-3) / 1e9
+    roofline_prepass = {
+        "bound": "hbm", "kernel": "prepass (all launches of one call)", "achieved": prepass_gbs,
+        "peak": hbm_peak if hbm_peak else 6650.0, "unit": "GB/s",
+        "frac": prepass_gbs / (hbm_peak if hbm_peak else 6650.0), "algorithmic_bytes": prepass_bytes,
+        "peak_note": "measured copy bandwidth; of measured" if hbm_peak else "of fallback", "ms": prep_ms,
+    }
+    # The reference's benchmark counts Sq(Sq+1)/2 query-key pairs for causal problems.
+    causal_pairs_value = None
+    if w.causal:
+        causal_pairs_value = world * 4.0 * w.flat_heads * w.head_dim * (w.q_len * (w.q_len + 1) / 2) / (ms * 1e-3) / 1e12
     cpu_baseline = None
     if world == 1 and not args.no_cpu_baseline:
         threads = os.cpu_count() or 1
@@ -328,7 +344,7 @@ def ours_arm(args, w, rank, local_rank, world):
         "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "int8",
         "data": "synthetic", "config": workload_config(w, world), "clocks": clocks, "e2e": e2e,
         "gpu_launches": (prepass_launches + 1) * args.steps, "roofline": roofline, "cpu_baseline": cpu_baseline,
-        "device_status": status[0],
+        "roofline_prepass": roofline_prepass, "value_causal_pairs": causal_pairs_value, "device_status": status[0],
     }
     print(json.dumps(line), file=_JSON_OUT or sys.stdout, flush=True)
     if dist is not None:
