@@ -200,7 +200,8 @@ __global__ void __launch_bounds__(kThreads) row_range_kernel(TensorArg v, const 
 
 // ---------------------------------------------------------------------------------------
 // Stable ascending sort of one head's keys: least-significant-digit radix sort, 8 bits per
-// pass, one CTA per head.  After four passes the row indices are in idx_a ("order").
+// pass, one CTA per head; passes over a digit that all keys share are skipped (the sign and high
+// exponent bits of a row range usually are).  The row indices end in idx0 ("order").
 // ---------------------------------------------------------------------------------------
 constexpr int kSortThreads = 1024;
 
@@ -208,38 +209,52 @@ __global__ void __launch_bounds__(kSortThreads) segment_sort_kernel(uint32_t* __
                                                                     uint32_t* __restrict__ keys1,
                                                                     int32_t* __restrict__ idx0,
                                                                     int32_t* __restrict__ idx1, int n) {
+  __shared__ uint32_t hist[4][256];  // digit histograms of all four passes, from one read of the keys
   __shared__ uint32_t base[256];
   __shared__ uint32_t warp_cnt[kSortThreads / 32][256];
+  __shared__ int uniform[4];         // a digit on which every key agrees needs no pass
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const long long seg = static_cast<long long>(blockIdx.x) * n;
   uint32_t* kbuf[2] = {keys0 + seg, keys1 + seg};
   int32_t* ibuf[2] = {idx0 + seg, idx1 + seg};
 
+  for (int i = tid; i < 4 * 256; i += kSortThreads) (&hist[0][0])[i] = 0;
+  if (tid < 4) uniform[tid] = 0;
+  __syncthreads();
+  for (int i = tid; i < n; i += kSortThreads) {
+    const uint32_t key = kbuf[0][i];
+#pragma unroll
+    for (int d = 0; d < 4; ++d) atomicAdd(&hist[d][(key >> (8 * d)) & 0xFF], 1u);
+  }
+  __syncthreads();
+  for (int i = tid; i < 4 * 256; i += kSortThreads)
+    if ((&hist[0][0])[i] == static_cast<uint32_t>(n)) uniform[i >> 8] = 1;
+  __syncthreads();
+
+  int cur = 0;        // which buffer pair holds the current order
+  bool first = true;  // the first pass that runs reads the implicit identity permutation
   for (int pass = 0; pass < 4; ++pass) {
-    const uint32_t* ksrc = kbuf[pass & 1];
-    uint32_t* kdst = kbuf[(pass & 1) ^ 1];
-    const int32_t* isrc = ibuf[pass & 1];  // pass 0 reads the implicit identity instead
-    int32_t* idst = ibuf[(pass & 1) ^ 1];  // passes write idx1, idx0, idx1, idx0
+    if (uniform[pass]) continue;  // block-uniform decision
+    const uint32_t* ksrc = kbuf[cur];
+    uint32_t* kdst = kbuf[cur ^ 1];
+    const int32_t* isrc = ibuf[cur];
+    int32_t* idst = ibuf[cur ^ 1];
     const int shift = pass * 8;
 
-    if (tid < 256) base[tid] = 0;
-    __syncthreads();
-    for (int i = tid; i < n; i += kSortThreads) atomicAdd(&base[(ksrc[i] >> shift) & 0xFF], 1u);
-    __syncthreads();
     if (warp == 0) {  // exclusive scan of 256 counters, 8 per lane
-      uint32_t c[8], s = 0;
+      uint32_t c[8], sum = 0;
 #pragma unroll
       for (int i = 0; i < 8; ++i) {
-        c[i] = base[lane * 8 + i];
-        s += c[i];
+        c[i] = hist[pass][lane * 8 + i];
+        sum += c[i];
       }
-      uint32_t incl = s;
+      uint32_t incl = sum;
 #pragma unroll
       for (int o = 1; o < 32; o <<= 1) {
         const uint32_t t = __shfl_up_sync(0xffffffffu, incl, o);
         if (lane >= o) incl += t;
       }
-      uint32_t run = incl - s;
+      uint32_t run = incl - sum;
 #pragma unroll
       for (int i = 0; i < 8; ++i) {
         base[lane * 8 + i] = run;
@@ -256,7 +271,7 @@ __global__ void __launch_bounds__(kSortThreads) segment_sort_kernel(uint32_t* __
       uint32_t digit = 256;
       if (valid) {
         key = ksrc[i];
-        idx = (pass == 0) ? i : isrc[i];
+        idx = first ? i : isrc[i];
         digit = (key >> shift) & 0xFF;
       }
 #pragma unroll
@@ -284,6 +299,14 @@ __global__ void __launch_bounds__(kSortThreads) segment_sort_kernel(uint32_t* __
       }
       __syncthreads();
     }
+    cur ^= 1;
+    first = false;
+  }
+  // the order is read from idx0
+  if (first) {
+    for (int i = tid; i < n; i += kSortThreads) ibuf[0][i] = i;
+  } else if (cur == 1) {
+    for (int i = tid; i < n; i += kSortThreads) ibuf[0][i] = ibuf[1][i];
   }
 }
 
@@ -294,6 +317,18 @@ __global__ void __launch_bounds__(kSortThreads) segment_sort_kernel(uint32_t* __
 // ---------------------------------------------------------------------------------------
 __device__ __forceinline__ int round_clamp_i8(float x, float s) {
   const float q = rintf(__fdiv_rn(x, s));
+  return static_cast<int>(fminf(fmaxf(q, -127.f), 127.f));
+}
+
+// Same result as round_clamp_i8(x, s) with r = fl(1 / s), without the IEEE division in the common
+// case.  |x / s| < 128, so t = fl(x * r) is within 128 * (2^-24 + 2^-24) < 1.6e-5 of x / s, and the
+// correctly rounded quotient within 7.7e-6 of it: when t is at least 1e-4 away from every
+// half-integer, rint(t) equals rint(fl(x / s)); otherwise (about one element in 5000) the
+// division is done.
+__device__ __forceinline__ int round_clamp_i8_rcp(float x, float s, float r) {
+  const float t = x * r;
+  float q = rintf(t);
+  if (fabsf(fabsf(t - q) - 0.5f) < 1e-4f) q = rintf(__fdiv_rn(x, s));
   return static_cast<int>(fminf(fmaxf(q, -127.f), 127.f));
 }
 
@@ -380,12 +415,13 @@ __global__ void __launch_bounds__(kThreads) quantize_qk_kernel(
     const int r = blk * kBlockRows + lr;
     if (r >= len_pad) continue;
     const float s = row_scale[lr];
+    const float rs = __fdiv_rn(1.f, s);
     uint32_t w[2];
 #pragma unroll
     for (int h = 0; h < 2; ++h) {
       uint32_t acc = 0;
 #pragma unroll
-      for (int i = 0; i < 4; ++i) acc |= (static_cast<uint32_t>(round_clamp_i8(vals[p][h * 4 + i], s)) & 0xFFu) << (8 * i);
+      for (int i = 0; i < 4; ++i) acc |= (static_cast<uint32_t>(round_clamp_i8_rcp(vals[p][h * 4 + i], s, rs)) & 0xFFu) << (8 * i);
       w[h] = acc;
     }
     *reinterpret_cast<uint2*>(codes + (static_cast<long long>(bh) * len_pad + r) * D + cg * 8) = make_uint2(w[0], w[1]);
@@ -451,8 +487,9 @@ __global__ void __launch_bounds__(kThreads) quantize_v_kernel(
           col_inv[o] = 0.f;
         }
       }
+      const float rs = __fdiv_rn(1.f, s);
 #pragma unroll
-      for (int i = 0; i < 8; ++i) tile[(cg * 8 + i) * LD + lr] = static_cast<uint8_t>(round_clamp_i8(x[i], s) & 0xFF);
+      for (int i = 0; i < 8; ++i) tile[(cg * 8 + i) * LD + lr] = static_cast<uint8_t>(round_clamp_i8_rcp(x[i], s, rs) & 0xFF);
     } else {
       if (cg == 0) col_add[static_cast<long long>(bh) * sk_pad + r] = (r < sk) ? 0.f : -INFINITY;
 #pragma unroll
