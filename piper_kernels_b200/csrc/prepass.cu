@@ -440,9 +440,13 @@ __global__ void __launch_bounds__(kThreads) quantize_v_kernel(
     float* __restrict__ col_inv, int sk, int sk_pad, int heads) {
   constexpr int TPR = D / 8;
   constexpr int RPP = kThreads / TPR;
-  constexpr int NP = kBlockRows / RPP;
-  constexpr int LD = kBlockRows + 16;  // padded tile row, multiple of 16 bytes
-  __shared__ __align__(16) uint8_t tile[D * LD];
+  constexpr int NP = kBlockRows / RPP;  // adjacent keys per thread: 4 (head_dim 128) or 2 (64)
+  constexpr int WPR = kBlockRows / 4;   // 32-bit words per feature row of the transposed tile
+  static_assert(NP == 4 || NP == 2, "a thread's keys fill a word or half a word");
+  // Transposed tile [feature][64 keys]; a thread owns NP adjacent keys, so it writes one (half) word
+  // per feature.  The word position is rotated by the feature group so that the 16 (8) threads that
+  // hold the same keys of different feature groups hit different banks.
+  __shared__ __align__(16) uint32_t tile[D * WPR];
   const int bh = blockIdx.y, blk = blockIdx.x;
   const int cg = threadIdx.x % TPR, rl = threadIdx.x / TPR;
   const T* vp = static_cast<const T*>(head_ptr(v, bh, heads, sizeof(T)));
@@ -451,9 +455,12 @@ __global__ void __launch_bounds__(kThreads) quantize_v_kernel(
 #pragma unroll
   for (int i = 0; i < 8; ++i) aux[i] = v_mean_or_scale[bh * D + cg * 8 + i];
 
+  uint32_t packed[8];
+#pragma unroll
+  for (int i = 0; i < 8; ++i) packed[i] = 0;
 #pragma unroll
   for (int p = 0; p < NP; ++p) {
-    const int lr = p * RPP + rl;
+    const int lr = rl * NP + p;
     const int r = blk * kBlockRows + lr;
     float x[8];
     float m = 0.f;
@@ -476,34 +483,44 @@ __global__ void __launch_bounds__(kThreads) quantize_v_kernel(
 #pragma unroll
       for (int o = TPR / 2; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
       const float s = __fadd_rn(__fdiv_rn(m, 127.f), 1e-7f);
+      const float rs = __fdiv_rn(1.f, s);
       if (cg == 0) {
         const long long o = static_cast<long long>(bh) * sk_pad + r;
         if (r < sk) {
           v_scale[static_cast<long long>(bh) * sk + r] = s;
           col_add[o] = log2f(s);
-          col_inv[o] = __fdiv_rn(1.f, s);
+          col_inv[o] = rs;
         } else {
           col_add[o] = -INFINITY;
           col_inv[o] = 0.f;
         }
       }
-      const float rs = __fdiv_rn(1.f, s);
 #pragma unroll
-      for (int i = 0; i < 8; ++i) tile[(cg * 8 + i) * LD + lr] = static_cast<uint8_t>(round_clamp_i8_rcp(x[i], s, rs) & 0xFF);
+      for (int i = 0; i < 8; ++i) packed[i] |= (static_cast<uint32_t>(round_clamp_i8_rcp(x[i], s, rs)) & 0xFFu) << (8 * p);
     } else {
       if (cg == 0) col_add[static_cast<long long>(bh) * sk_pad + r] = (r < sk) ? 0.f : -INFINITY;
 #pragma unroll
       for (int i = 0; i < 8; ++i) {
         const float q = __fdiv_rn(x[i], aux[i]);
-        tile[(cg * 8 + i) * LD + lr] = static_cast<uint8_t>(__nv_cvt_float_to_fp8(q, __NV_SATFINITE, __NV_E4M3));
+        packed[i] |= static_cast<uint32_t>(__nv_cvt_float_to_fp8(q, __NV_SATFINITE, __NV_E4M3)) << (8 * p);
       }
     }
   }
+  {
+    const int key0 = rl * NP;                   // first of this thread's keys within the tile
+    const int word = ((key0 >> 2) + cg) % WPR;  // rotated word position
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      uint32_t* row = tile + (cg * 8 + i) * WPR;
+      if (NP == 4) row[word] = packed[i];
+      else reinterpret_cast<uint16_t*>(row)[word * 2 + ((key0 >> 1) & 1)] = static_cast<uint16_t>(packed[i]);
+    }
+  }
   __syncthreads();
-  for (int idx = threadIdx.x; idx < D * 4; idx += kThreads) {
-    const int d = idx >> 2, c = idx & 3;
-    const uint4 val = *reinterpret_cast<const uint4*>(&tile[d * LD + c * 16]);
-    *reinterpret_cast<uint4*>(codes_t + (static_cast<long long>(bh) * D + d) * sk_pad + blk * kBlockRows + c * 16) = val;
+  for (int idx = threadIdx.x; idx < D * WPR; idx += kThreads) {
+    const int d = idx / WPR, w = idx % WPR;
+    const uint32_t val = tile[d * WPR + (w + d / 8) % WPR];
+    *reinterpret_cast<uint32_t*>(codes_t + (static_cast<long long>(bh) * D + d) * sk_pad + blk * kBlockRows + w * 4) = val;
   }
 }
 
