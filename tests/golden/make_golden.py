@@ -19,7 +19,7 @@ from pathlib import Path
 import numpy as np
 import torch
 
-REF = os.environ.get("PIPER_REF_SRC", "/root/reference/src")
+REF = os.environ["PIPER_REF_SRC"]  # path of the reference project's src/ directory
 sys.path.insert(0, REF)
 
 from piper_kernels.attention.kernels.qk_quantization.int8.sage.reference import (  # noqa: E402

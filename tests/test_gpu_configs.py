@@ -1,4 +1,4 @@
-"""GPU parity on the benchmark configurations (BASELINE.json's five shapes) and on the
+"""GPU parity on the benchmark configurations (the five benchmark shapes c1-c5) and on the
 host-pipelined entry point.  Whole tensors are compared where the oracle finishes in seconds;
 for the large shapes one head is run on the GPU at full length and a block of query rows is
 compared with the oracle (rows are independent given the head's K/V), plus size-independent
