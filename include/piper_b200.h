@@ -50,7 +50,9 @@ extern "C" {
 
 /* One attention call.  Tensors are [batch, heads, sequence, head_dim] with a contiguous head
  * dimension; strides are in elements for batch, head and sequence.  q/k/v are borrowed and
- * never written.  `out` is contiguous [batch, heads, q_len, head_dim]. */
+ * never written.  `out` is contiguous [batch, heads, q_len, head_dim].
+ * Limits: batch*heads <= 65535 (it is a grid dimension; split larger calls over the batch) and
+ * batch*heads*(sequence rounded up to a tile) < 2^31 rows. */
 typedef struct pk_problem {
   int32_t batch, heads, q_len, kv_len, head_dim; /* head_dim 64 or 128 */
   int32_t in_dtype;                              /* PK_F16 | PK_BF16 */
@@ -103,6 +105,16 @@ PK_API const char* pk_last_error(void);
 PK_API int pk_piper_workspace_bytes(const pk_problem* p, uint64_t* bytes);
 PK_API int pk_piper_prepare(const pk_problem* p, pk_views* views); /* prepass only (piper/triton.py:1054-1236) */
 PK_API int pk_piper_run(const pk_problem* p);                      /* fused kernel on a prepared workspace (:1239-1289) */
+/* Prepared key/value reuse: the reference's benchmarks split every provider into prepare() and
+ * run(prepared) (benchmarks/lib/attention_providers.py:201-216); cross-attention and diffusion
+ * steps keep K/V and change only the queries.  pk_*_prepare_kv quantises the key/value side into
+ * the workspace once (means, key order, K and V codes, per-key vectors: piper/triton.py:744-836,
+ * 1119-1195; q is not read).  pk_*_prepare_q quantises a query batch of the same shape into the
+ * same workspace (Q codes and row multipliers: piper/triton.py:839-973; k and v are not read but
+ * must stay non-null).  Any sequence prepare_kv, then (prepare_q, run)* equals the same number
+ * of full calls bit for bit. */
+PK_API int pk_piper_prepare_kv(const pk_problem* p, pk_views* views);
+PK_API int pk_piper_prepare_q(const pk_problem* p, pk_views* views);
 PK_API int pk_piper_attention_fwd(const pk_problem* p);            /* prepare + run */
 
 /* SageAttention2++ (8+8).  Replaces _run_sage_attention_2pp (sage2pp/triton.py:446-679)
@@ -110,11 +122,22 @@ PK_API int pk_piper_attention_fwd(const pk_problem* p);            /* prepare + 
 PK_API int pk_sage2pp_workspace_bytes(const pk_problem* p, uint64_t* bytes);
 PK_API int pk_sage2pp_prepare(const pk_problem* p, pk_views* views);
 PK_API int pk_sage2pp_run(const pk_problem* p);
+PK_API int pk_sage2pp_prepare_kv(const pk_problem* p, pk_views* views); /* K mean, V channel scale, K / V codes (sage2pp/triton.py:478-518, 631-647) */
+PK_API int pk_sage2pp_prepare_q(const pk_problem* p, pk_views* views);  /* Q codes (sage2pp/triton.py:539-630) */
 PK_API int pk_sage2pp_attention_fwd(const pk_problem* p);
 
 /* Copies the 16 status words of the workspace to the host after synchronising the stream.
- * status[0] != 0 means a kernel abandoned a wait (the value says which one). */
+ * status[0] != 0 means a kernel abandoned a wait (the value says which one); the output rows of
+ * the query tiles that gave up hold NaN. */
 PK_API int pk_device_status(const pk_problem* p, int32_t status[16]);
+
+/* Non-blocking check for the same condition, for callers that do not keep the workspace (the
+ * torch operators): every fused kernel also writes its wait-site code into one pinned host word
+ * per device; this call reads and clears it without touching the device or any stream.  Returns
+ * PK_ERR_DEVICE_STATUS with *code != 0 when a kernel launched earlier on `device` gave up a
+ * wait, PK_OK with *code == 0 otherwise.  The reference has no counterpart (its kernels cannot
+ * give up a wait); it stands where the reference relies on CUDA's own launch errors. */
+PK_API int pk_poll_device_fault(int32_t device, int32_t* code);
 
 /* Debug aid for parity tests: runs the fused kernel and also copies the raw INT32 score tile
  * (first 64 keys, [128,64]), the packed probability codes ([128,64] bytes) and the raw PV
@@ -124,9 +147,18 @@ PK_API int pk_debug_first_tile(const pk_problem* p, int sage, int bh, int q_tile
 
 /* Profiling aid: runs the ordinary fused kernel and records, for the CTA of query tile `q_tile`
  * of flattened head `bh`, clock64() stamps of every warp role per key tile into `stamps`
- * (device memory, int64 [7 roles][max_tiles][8]; roles: the softmax warpgroups first - two at
- * head_dim 128, three at head_dim 64 - then dequant, S-product issue, PV-product issue). */
+ * (device memory, int64 [7 roles][max_tiles][8]; roles: the two softmax warpgroups, then
+ * dequant, S-product issue, PV-product issue). */
 PK_API int pk_debug_timeline(const pk_problem* p, int sage, int bh, int q_tile, void* stamps, int max_tiles);
+
+/* Stalled-wait drill (test aid).  Runs the fused kernel on a prepared workspace with the copy of
+ * key tile `skip_key_tile` left out by every CTA's producer and with every wait limited to about
+ * 0.1 ms: the wait for that tile expires, every warp role unwinds, copies in flight are drained,
+ * tensor memory is released and the kernel returns normally.  Afterwards pk_device_status and
+ * pk_poll_device_fault report the wait site (22: the S-product issue warp waiting for a K tile),
+ * the affected output rows hold NaN, and the device and context remain usable.  Nothing traps,
+ * faults or spins without a limit. */
+PK_API int pk_debug_stalled_wait(const pk_problem* p, int sage, int skip_key_tile);
 
 /* K and V sequence means ([batch*heads, head_dim] f32 each, device memory) computed without a
  * workspace and without any allocation.  No counterpart in the reference: it exists for hosts

@@ -21,6 +21,8 @@ EXPORTS = (
     "pk_piper_workspace_bytes", "pk_piper_prepare", "pk_piper_run", "pk_piper_attention_fwd",
     "pk_sage2pp_workspace_bytes", "pk_sage2pp_prepare", "pk_sage2pp_run", "pk_sage2pp_attention_fwd",
     "pk_device_status", "pk_debug_first_tile", "pk_kv_means_static", "pk_debug_timeline",
+    "pk_piper_prepare_kv", "pk_piper_prepare_q", "pk_sage2pp_prepare_kv", "pk_sage2pp_prepare_q",
+    "pk_poll_device_fault", "pk_debug_stalled_wait",
 )
 
 
@@ -73,7 +75,8 @@ def lib() -> C.CDLL:
         handle.pk_last_error.restype = C.c_char_p
         for name in ("pk_piper_workspace_bytes", "pk_sage2pp_workspace_bytes"):
             getattr(handle, name).argtypes = [P, C.POINTER(C.c_uint64)]
-        for name in ("pk_piper_prepare", "pk_sage2pp_prepare"):
+        for name in ("pk_piper_prepare", "pk_sage2pp_prepare", "pk_piper_prepare_kv", "pk_piper_prepare_q",
+                     "pk_sage2pp_prepare_kv", "pk_sage2pp_prepare_q"):
             getattr(handle, name).argtypes = [P, V]
         for name in ("pk_piper_run", "pk_piper_attention_fwd", "pk_sage2pp_run", "pk_sage2pp_attention_fwd"):
             getattr(handle, name).argtypes = [P]
@@ -81,6 +84,8 @@ def lib() -> C.CDLL:
         handle.pk_debug_first_tile.argtypes = [P, C.c_int, C.c_int, C.c_int, C.c_void_p]
         handle.pk_debug_timeline.argtypes = [P, C.c_int, C.c_int, C.c_int, C.c_void_p, C.c_int]
         handle.pk_kv_means_static.argtypes = [P, C.c_void_p, C.c_void_p]
+        handle.pk_poll_device_fault.argtypes = [C.c_int32, C.POINTER(C.c_int32)]
+        handle.pk_debug_stalled_wait.argtypes = [P, C.c_int, C.c_int]
         for name in EXPORTS[2:]:
             getattr(handle, name).restype = C.c_int
         _lib = handle

@@ -66,10 +66,19 @@ def _require_cuda(t: torch.Tensor, name: str) -> None:
             f"piper_b200::{name} runs only on CUDA tensors (B200, sm_100a); there is no CPU path")
 
 
+def poll_device_fault(device_index: int) -> None:
+    """Raise if a fused kernel launched earlier on this device gave up a bounded wait (its output
+    rows were filled with NaN).  Reads one pinned host word: no synchronisation, no device work."""
+    code = C.c_int32(0)
+    _cabi.check(_cabi.lib().pk_poll_device_fault(int(device_index), C.byref(code)))
+
+
 def _run(algo: str, query, key, value, scale, is_causal, center_value, sort_value_rows, granularity):
     _require_cuda(query, algo)
     out = torch.empty(query.shape, dtype=query.dtype, device=query.device)
     with torch.cuda.device(query.device):
+        dev_index = query.device.index if query.device.index is not None else torch.cuda.current_device()
+        poll_device_fault(dev_index)
         p = make_problem(query, key, value, scale, is_causal, center_value=center_value,
                          sort_value_rows=sort_value_rows, granularity=granularity, out=out)
         ws = torch.empty(workspace_bytes(algo, p), dtype=torch.uint8, device=query.device)

@@ -4,6 +4,9 @@
 
 #include <math.h>
 #include <stdarg.h>
+
+#include <atomic>
+#include <mutex>
 #include <stdio.h>
 #include <string.h>
 
@@ -70,17 +73,54 @@ Layout make_layout(const pk_problem& p, Algo algo) {
   return L;
 }
 
+constexpr int kMaxDevices = 64;
+
 static int device_major(int device) {
-  static int cache[64];
-  static bool have[64];
-  if (device < 0 || device >= 64) return -1;
-  if (!have[device]) {
-    int major = 0;
-    if (cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, device) != cudaSuccess) return -1;
-    cache[device] = major;
-    have[device] = true;
+  // 0 = not yet queried; concurrent first calls store the same value
+  static std::atomic<int> cache[kMaxDevices];
+  if (device < 0 || device >= kMaxDevices) return -1;
+  int major = cache[device].load(std::memory_order_acquire);
+  if (major == 0) {
+    if (cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, device) != cudaSuccess || major <= 0) return -1;
+    cache[device].store(major, std::memory_order_release);
   }
-  return cache[device];
+  return major;
+}
+
+namespace {
+struct FaultWord {
+  std::once_flag once;
+  int32_t* host = nullptr;
+  int32_t* dev = nullptr;
+};
+FaultWord g_fault[kMaxDevices];
+
+FaultWord* fault_word(int device) {
+  if (device < 0 || device >= kMaxDevices) return nullptr;
+  FaultWord& f = g_fault[device];
+  std::call_once(f.once, [&f] {
+    void* h = nullptr;
+    if (cudaHostAlloc(&h, sizeof(int32_t), cudaHostAllocMapped | cudaHostAllocPortable) != cudaSuccess) {
+      cudaGetLastError();
+      return;
+    }
+    *static_cast<volatile int32_t*>(h) = 0;
+    void* d = nullptr;
+    if (cudaHostGetDevicePointer(&d, h, 0) != cudaSuccess) {
+      cudaGetLastError();
+      cudaFreeHost(h);
+      return;
+    }
+    f.host = static_cast<int32_t*>(h);
+    f.dev = static_cast<int32_t*>(d);
+  });
+  return &f;
+}
+}  // namespace
+
+int32_t* fault_word_device_ptr(int device) {
+  FaultWord* f = fault_word(device);
+  return f ? f->dev : nullptr;
 }
 
 int validate(const pk_problem* p, Algo algo, bool need_workspace) {
@@ -104,6 +144,9 @@ int validate(const pk_problem* p, Algo algo, bool need_workspace) {
       return fail(PK_ERR_BAD_ARG, "value-row ordering requires centered non-causal grouped-QK attention");
   }
   if (!p->q || !p->k || !p->v) return fail(PK_ERR_BAD_ARG, "%s: null input pointer", name);
+  if (static_cast<int64_t>(p->batch) * p->heads > 65535)
+    return fail(PK_ERR_BAD_ARG, "%s: batch*heads must not exceed 65535 (got %lld); split the call", name,
+                static_cast<long long>(p->batch) * p->heads);
   if (static_cast<int64_t>(p->batch) * p->heads * (static_cast<int64_t>(p->q_len) + 127) >= (1ll << 31) ||
       static_cast<int64_t>(p->batch) * p->heads * (static_cast<int64_t>(p->kv_len) + 63) >= (1ll << 31))
     return fail(PK_ERR_BAD_ARG, "%s: batch*heads*sequence must stay below 2^31 rows", name);
@@ -174,7 +217,7 @@ int workspace_bytes(const pk_problem* p, Algo algo, uint64_t* bytes) {
   return PK_OK;
 }
 
-int prepare(const pk_problem* p, Algo algo, pk_views* views) {
+int prepare(const pk_problem* p, Algo algo, pk_views* views, int parts = kPrepassAll) {
   g_err[0] = 0;
   int rc = validate(p, algo, true);
   if (rc) return rc;
@@ -182,7 +225,7 @@ int prepare(const pk_problem* p, Algo algo, pk_views* views) {
   if (g.err != cudaSuccess) return fail(PK_ERR_CUDA, "cudaSetDevice(%d): %s", p->device, cuda_err(g.err));
   if ((rc = check_arch(p))) return rc;
   const Layout L = make_layout(*p, algo);
-  if ((rc = launch_prepass(*p, L, algo, static_cast<cudaStream_t>(p->stream)))) return rc;
+  if ((rc = launch_prepass(*p, L, algo, static_cast<cudaStream_t>(p->stream), parts))) return rc;
   if (views) fill_views(*p, L, algo, views);
   return PK_OK;
 }
@@ -210,6 +253,8 @@ PK_API const char* pk_last_error(void) { return g_err; }
 
 PK_API int pk_piper_workspace_bytes(const pk_problem* p, uint64_t* bytes) { return workspace_bytes(p, kPiper, bytes); }
 PK_API int pk_piper_prepare(const pk_problem* p, pk_views* views) { return prepare(p, kPiper, views); }
+PK_API int pk_piper_prepare_kv(const pk_problem* p, pk_views* views) { return prepare(p, kPiper, views, kPrepassKV); }
+PK_API int pk_piper_prepare_q(const pk_problem* p, pk_views* views) { return prepare(p, kPiper, views, kPrepassQ); }
 PK_API int pk_piper_run(const pk_problem* p) { return run(p, kPiper, nullptr); }
 PK_API int pk_piper_attention_fwd(const pk_problem* p) {
   const int rc = prepare(p, kPiper, nullptr);
@@ -218,6 +263,8 @@ PK_API int pk_piper_attention_fwd(const pk_problem* p) {
 
 PK_API int pk_sage2pp_workspace_bytes(const pk_problem* p, uint64_t* bytes) { return workspace_bytes(p, kSage, bytes); }
 PK_API int pk_sage2pp_prepare(const pk_problem* p, pk_views* views) { return prepare(p, kSage, views); }
+PK_API int pk_sage2pp_prepare_kv(const pk_problem* p, pk_views* views) { return prepare(p, kSage, views, kPrepassKV); }
+PK_API int pk_sage2pp_prepare_q(const pk_problem* p, pk_views* views) { return prepare(p, kSage, views, kPrepassQ); }
 PK_API int pk_sage2pp_run(const pk_problem* p) { return run(p, kSage, nullptr); }
 PK_API int pk_sage2pp_attention_fwd(const pk_problem* p) {
   const int rc = prepare(p, kSage, nullptr);
@@ -250,14 +297,34 @@ PK_API int pk_kv_means_static(const pk_problem* p, float* k_mean, float* v_mean)
 
 PK_API int pk_debug_first_tile(const pk_problem* p, int sage, int bh, int q_tile, void* dump) {
   if (!dump) return fail(PK_ERR_BAD_ARG, "pk_debug_first_tile: null dump pointer");
-  const DebugDump d{dump, bh, q_tile, nullptr, 0};
+  const DebugDump d{dump, bh, q_tile, nullptr, 0, -1};
   return run(p, sage ? kSage : kPiper, &d);
 }
 
 PK_API int pk_debug_timeline(const pk_problem* p, int sage, int bh, int q_tile, void* stamps, int max_tiles) {
   if (!stamps || max_tiles <= 0) return fail(PK_ERR_BAD_ARG, "pk_debug_timeline: null buffer");
-  const DebugDump d{nullptr, bh, q_tile, stamps, max_tiles};
+  const DebugDump d{nullptr, bh, q_tile, stamps, max_tiles, -1};
   return run(p, sage ? kSage : kPiper, &d);
+}
+
+PK_API int pk_debug_stalled_wait(const pk_problem* p, int sage, int skip_key_tile) {
+  if (skip_key_tile < 0) return fail(PK_ERR_BAD_ARG, "pk_debug_stalled_wait: key tile index must be >= 0");
+  const DebugDump d{nullptr, -1, -1, nullptr, 0, skip_key_tile};
+  return run(p, sage ? kSage : kPiper, &d);
+}
+
+PK_API int pk_poll_device_fault(int device, int32_t* code) {
+  g_err[0] = 0;
+  if (!code) return fail(PK_ERR_BAD_ARG, "pk_poll_device_fault: null argument");
+  *code = 0;
+  if (device < 0 || device >= kMaxDevices) return fail(PK_ERR_BAD_ARG, "pk_poll_device_fault: bad device %d", device);
+  // The word exists only after a launch on this device; nothing to report before that.
+  FaultWord& f = g_fault[device];
+  if (f.host == nullptr) return PK_OK;
+  const int32_t v = __atomic_exchange_n(f.host, 0, __ATOMIC_ACQ_REL);
+  *code = v;
+  if (v != 0) return fail(PK_ERR_DEVICE_STATUS, "an earlier fused kernel on device %d abandoned wait site %d; its output rows were filled with NaN", device, v);
+  return PK_OK;
 }
 
 }  // extern "C"

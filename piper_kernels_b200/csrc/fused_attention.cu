@@ -53,6 +53,46 @@
 #ifndef PK_DQ_STAT_AT
 #define PK_DQ_STAT_AT 1
 #endif
+// deferred conversion bias: fold y*c directly (y = 1.5*2^23 + partial) and subtract the accumulated
+// 1.5*2^23 * sum(c) every PK_DQ_BIAS_GROUP tiles (0: subtract the bias from every word first)
+#ifndef PK_DQ_BIAS_GROUP
+#define PK_DQ_BIAS_GROUP 0
+#endif
+// release partial buffer j while tile j+1 is being folded instead of at the end of tile j
+#ifndef PK_DQ_LATE_RELEASE
+#define PK_DQ_LATE_RELEASE 0
+#endif
+// softmax re-reads the arming block from shared memory each tile instead of keeping 16 registers live
+#ifndef PK_SM_ARM_RELOAD
+#define PK_SM_ARM_RELOAD 0
+#endif
+#ifndef PK_DQ_NEXT_AT
+#define PK_DQ_NEXT_AT -1
+#endif
+#ifndef PK_ABL_STATS
+#define PK_ABL_STATS 0
+#endif
+#ifndef PK_ABL_DQARM
+#define PK_ABL_DQARM 0
+#endif
+#ifndef PK_ABL_V
+#define PK_ABL_V 0
+#endif
+#ifndef PK_ABL_VEC
+#define PK_ABL_VEC 0
+#endif
+#ifndef PK_ABL_K
+#define PK_ABL_K 0
+#endif
+#ifndef PK_ABL_SMARM
+#define PK_ABL_SMARM 0
+#endif
+#ifndef PK_ABL_SM
+#define PK_ABL_SM 0
+#endif
+#ifndef PK_ABL_DQ
+#define PK_ABL_DQ 0
+#endif
 #ifndef PK_NSWG_PIPER
 #define PK_NSWG_PIPER 2
 #endif
@@ -110,6 +150,8 @@ struct FusedParams {
   int dump_bh, dump_qt;
   long long* timeline;  // optional [6][timeline_tiles][4] clock stamps of CTA (dump_bh, dump_qt)
   int timeline_tiles;
+  int skip_key_tile;        // stalled-wait drill only: key tile whose copy the producer leaves out
+  int32_t* host_status;     // optional pinned host word (device-visible) that also receives the code
 };
 
 template <int D, int ALGO>
@@ -222,6 +264,13 @@ fused_attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
   const bool causal = (CAUSAL == 2) ? (prm.causal != 0) : (CAUSAL == 1);
   constexpr bool DUMP = DEBUG == 1;      // copy out the first key tile's intermediates
   constexpr bool TIMELINE = DEBUG == 2;  // per-role clock stamps of one CTA
+  // DEBUG == 3: the stalled-wait drill.  The producer leaves out the copy of one key tile (a
+  // host-chosen index), so the wait for it can never be satisfied, and every wait gives up after
+  // a tenth of a millisecond instead of most of a second: the whole unwind path runs (abort flag,
+  // votes around the warp-synchronous instructions, drain of copies in flight, tensor-memory
+  // release, status word) while the GPU and the context stay healthy.
+  constexpr bool DRILL = DEBUG == 3;
+  constexpr long long kLimit = DRILL ? 200000LL : kWaitCycleLimit;
   constexpr bool O_MAGIC = (ALGO == kPiper);  // the sage partial is FP32 and needs no conversion
   extern __shared__ uint8_t smem_raw[];
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -278,19 +327,25 @@ fused_attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
 
   if (warp == PROD_WARP) {
     // ------------------------------------------------------------------ producer
-    if (lane == 0) {
+    // All 32 lanes run the loop and the waits; the elected lane issues the copies.
+    if (elect_one()) {
       prefetch_tmap(&tm_q); prefetch_tmap(&tm_k); prefetch_tmap(&tm_v);
       mbar_expect_tx(bars.q_full(), C::Q_BYTES);
       tma_load_2d(smem_base + C::OFF_Q, &tm_q, bars.q_full(), 0, bh * prm.sq_pad + q0);
-      const long long vec_base = static_cast<long long>(bh) * prm.sk_pad;
-      for (int i = 0; i < n_tiles + V_LAG; ++i) {
-        if (i < n_tiles) {
-          const int s = i % NK;
-          if (i >= NK && !mbar_wait_bounded(bars.qk_done(s), ((i / NK) - 1) & 1, abort_flag, W_PROD_K)) break;
-          {
+    }
+    const long long vec_base = static_cast<long long>(bh) * prm.sk_pad;
+    int last_k = -1, last_v = -1;  // last key tile / value tile whose copy was issued
+    for (int i = 0; i < n_tiles + V_LAG; ++i) {
+      if (i < n_tiles) {
+        const int s = i % NK;
+        if (i >= NK && !WARP_ALL(mbar_wait_bounded(bars.qk_done(s), ((i / NK) - 1) & 1, abort_flag, W_PROD_K, kLimit))) break;
+        if (elect_one()) {
+          if ((!PK_ABL_K || i < NK) && !(DRILL && i == prm.skip_key_tile)) {
           mbar_expect_tx(bars.k_full(s), C::K_BYTES);
           tma_load_2d(smem_base + C::OFF_K + s * C::K_BYTES, &tm_k, bars.k_full(s), 0,
                       bh * prm.sk_pad + i * kKeyTile);
+          }
+          if (!PK_ABL_VEC) {
           // The vector slot of tile i-NVEC was last read before the probabilities of that tile
           // were published, which precedes the issue (and so the completion) of the K stage
           // release waited for above (NVEC >= NK + NS + 2).
@@ -304,65 +359,77 @@ fused_attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
           bulk_load(vdst + 2 * kKeyTile * 4, prm.k_inv + off, kKeyTile * 4, vbar);
           }
         }
-        const int j = i - V_LAG;
-        if (j >= 0 && j < n_tiles) {
-          const int s = j % NV;
-          if (j >= NV && !mbar_wait_bounded(bars.pv_done(s), ((j / NV) - 1) & 1, abort_flag, W_PROD_V)) break;
-          {
-            mbar_expect_tx(bars.v_full(s), C::V_BYTES);
-            tma_load_2d(smem_base + C::OFF_V + s * C::V_BYTES, &tm_v, bars.v_full(s), j * kKeyTile, bh * D);
-          }
-        }
+        last_k = i;
       }
+      const int j = i - V_LAG;
+      if (j >= 0 && j < n_tiles) {
+        const int s = j % NV;
+        if (j >= NV && !WARP_ALL(mbar_wait_bounded(bars.pv_done(s), ((j / NV) - 1) & 1, abort_flag, W_PROD_V, kLimit))) break;
+        if (!PK_ABL_V && elect_one()) {
+          mbar_expect_tx(bars.v_full(s), C::V_BYTES);
+          tma_load_2d(smem_base + C::OFF_V + s * C::V_BYTES, &tm_v, bars.v_full(s), j * kKeyTile, bh * D);
+        }
+        last_v = j;
+      }
+    }
+    if (*abort_flag != 0) {
+      // Giving up: let the copies this warp has issued land (each wait is short and raises nothing)
+      // before the CTA returns and its shared memory is handed to another CTA.
+      constexpr long long kDrain = 100000;
+      mbar_wait_quiet(bars.q_full(), 0, kDrain);
+      for (int t = max(0, last_k - NK + 1); t <= last_k; ++t) {
+        if (!(DRILL && t == prm.skip_key_tile)) mbar_wait_quiet(bars.k_full(t % NK), (t / NK) & 1, kDrain);
+      }
+      for (int t = max(0, last_k - NVEC + 1); t <= last_k; ++t) mbar_wait_quiet(bars.vec_full(t % NVEC), (t / NVEC) & 1, kDrain);
+      for (int t = max(0, last_v - NV + 1); t <= last_v; ++t) mbar_wait_quiet(bars.v_full(t % NV), (t / NV) & 1, kDrain);
     }
   } else if (warp == QK_WARP) {
     // ------------------------------------------------------------------ S = Q K^T issue
-    // tcgen05.mma issue costs tens of cycles per instruction, so the two products are issued
-    // by two different warps.  S_j is issued as soon as K tile j has landed and score buffer
-    // j % NS has been read and re-armed by the softmax warpgroup.
-    if (lane == 0) {
-      constexpr uint32_t idesc_qk = umma_idesc(kAccS32, kFmtS8, kFmtS8, kQTile, kKeyTile);
-      const uint64_t qdesc = umma_smem_desc(smem_base + C::OFF_Q, D);
-      const uint64_t kdesc0 = umma_smem_desc(smem_base + C::OFF_K, D);
-      bool ok = mbar_wait_bounded(bars.q_full(), 0, abort_flag, W_QK_Q);
-      for (int j = 0; ok && j < n_tiles; ++j) {
-        PK_STAMP(NSWG + 1, j, 0);
-        if (!mbar_wait_bounded(bars.k_full(j % NK), (j / NK) & 1, abort_flag, W_QK_K)) break;
-        if (!mbar_wait_bounded(bars.s_free(j % NS), (j / NS) & 1, abort_flag, W_QK_S)) break;
-        tc_fence_after();
-        PK_STAMP(NSWG + 1, j, 1);
-        const uint64_t kdesc = kdesc0 + static_cast<uint64_t>(((j % NK) * C::K_BYTES) >> 4);
-        const uint32_t d = tmem_base + C::COL_S + (j % NS) * kKeyTile;
+    // The two products are issued by two different warps.  S_j is issued as soon as K tile j has
+    // landed and score buffer j % NS has been read and re-armed by the softmax warpgroup.
+    constexpr uint32_t idesc_qk = umma_idesc(kAccS32, kFmtS8, kFmtS8, kQTile, kKeyTile);
+    const uint64_t qdesc = umma_smem_desc(smem_base + C::OFF_Q, D);
+    const uint64_t kdesc0 = umma_smem_desc(smem_base + C::OFF_K, D);
+    bool ok = WARP_ALL(mbar_wait_bounded(bars.q_full(), 0, abort_flag, W_QK_Q, kLimit));
+    for (int j = 0; ok && j < n_tiles; ++j) {
+      PK_STAMP(NSWG + 1, j, 0);
+      if ((!PK_ABL_K || j < NK) && !WARP_ALL(mbar_wait_bounded(bars.k_full(j % NK), (j / NK) & 1, abort_flag, W_QK_K, kLimit))) break;
+      if (!WARP_ALL(mbar_wait_bounded(bars.s_free(j % NS), (j / NS) & 1, abort_flag, W_QK_S, kLimit))) break;
+      tc_fence_after();
+      PK_STAMP(NSWG + 1, j, 1);
+      const uint64_t kdesc = kdesc0 + static_cast<uint64_t>(((j % NK) * C::K_BYTES) >> 4);
+      const uint32_t d = tmem_base + C::COL_S + (j % NS) * kKeyTile;
+      if (elect_one()) {
 #pragma unroll
         for (int kk = 0; kk < D / 32; ++kk) umma_i8_ss(d, qdesc + 2 * kk, kdesc + 2 * kk, idesc_qk, 1u);
         tc_commit(bars.qk_done(j % NK));
-        PK_STAMP(NSWG + 1, j, 2);
       }
+      PK_STAMP(NSWG + 1, j, 2);
     }
   } else if (warp == PV_WARP) {
     // ------------------------------------------------------------------ O_part = P V issue
-    if (lane == 0) {
-      constexpr uint32_t idesc_pv = (ALGO == kPiper) ? umma_idesc(kAccS32, kFmtU8, kFmtS8, kQTile, D)
-                                                     : umma_idesc(kAccF32, kFmtE4M3, kFmtE4M3, kQTile, D);
-      const uint64_t vdesc0 = umma_smem_desc(smem_base + C::OFF_V, kKeyTile);
-      for (int j = 0; j < n_tiles; ++j) {
-        PK_STAMP(NSWG + 2, j, 0);
-        if (!mbar_wait_bounded(bars.p_ready(j % NP), (j / NP) & 1, abort_flag, W_PV_P)) break;
-        if (!mbar_wait_bounded(bars.o_empty(j % NO), (j / NO) & 1, abort_flag, W_PV_O)) break;
-        if (!mbar_wait_bounded(bars.v_full(j % NV), (j / NV) & 1, abort_flag, W_PV_V)) break;
-        tc_fence_after();
-        PK_STAMP(NSWG + 2, j, 1);
-        const uint64_t vdesc = vdesc0 + static_cast<uint64_t>(((j % NV) * C::V_BYTES) >> 4);
-        const uint32_t d = tmem_base + C::COL_O + (j % NO) * D;
-        const uint32_t a = tmem_base + C::COL_P + (j % NP) * (kKeyTile / 4);
+    constexpr uint32_t idesc_pv = (ALGO == kPiper) ? umma_idesc(kAccS32, kFmtU8, kFmtS8, kQTile, D)
+                                                   : umma_idesc(kAccF32, kFmtE4M3, kFmtE4M3, kQTile, D);
+    const uint64_t vdesc0 = umma_smem_desc(smem_base + C::OFF_V, kKeyTile);
+    for (int j = 0; j < n_tiles; ++j) {
+      PK_STAMP(NSWG + 2, j, 0);
+      if (!WARP_ALL(mbar_wait_bounded(bars.p_ready(j % NP), (j / NP) & 1, abort_flag, W_PV_P, kLimit))) break;
+      if (!WARP_ALL(mbar_wait_bounded(bars.o_empty(j % NO), (j / NO) & 1, abort_flag, W_PV_O, kLimit))) break;
+      if (!PK_ABL_V && !WARP_ALL(mbar_wait_bounded(bars.v_full(j % NV), (j / NV) & 1, abort_flag, W_PV_V, kLimit))) break;
+      tc_fence_after();
+      PK_STAMP(NSWG + 2, j, 1);
+      const uint64_t vdesc = vdesc0 + static_cast<uint64_t>(((j % NV) * C::V_BYTES) >> 4);
+      const uint32_t d = tmem_base + C::COL_O + (j % NO) * D;
+      const uint32_t a = tmem_base + C::COL_P + (j % NP) * (kKeyTile / 4);
+      if (elect_one()) {
 #pragma unroll
         for (int kk = 0; kk < kKeyTile / 32; ++kk) {
           if (ALGO == kPiper) umma_i8_ts(d, a + 8 * kk, vdesc + 2 * kk, idesc_pv, 1u);
           else umma_f8_ts(d, a + 8 * kk, vdesc + 2 * kk, idesc_pv, kk > 0);
         }
         tc_commit(bars.pv_done(j % NP));
-        PK_STAMP(NSWG + 2, j, 2);
       }
+      PK_STAMP(NSWG + 2, j, 2);
     }
   } else if (wg < NSWG) {
     // ------------------------------------------------------------------ softmax
@@ -378,13 +445,15 @@ fused_attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
       for (int i = 0; i < NS; ++i) mbar_arrive(bars.s_free(i));
     }
     const float2 neg_magic2 = make_float2(-kMagic, -kMagic);
+#if !PK_SM_ARM_RELOAD
     uint32_t armv[16];
     load_arm_block(smem_base + C::OFF_MAGIC, armv);
+#endif
     for (int j = wg; j < n_tiles; j += NSWG) {
       PK_STAMP(wg, j, 0);
       // votes keep the warp converged for the .sync.aligned tensor-memory ops even when a wait is abandoned
-      if (!WARP_ALL(mbar_wait_bounded(bars.vec_full(j % NVEC), (j / NVEC) & 1, abort_flag, W_SM_VEC))) break;
-      if (!WARP_ALL(mbar_wait_bounded(bars.qk_done(j % NK), (j / NK) & 1, abort_flag, W_SM_S))) break;
+      if (!PK_ABL_VEC && !WARP_ALL(mbar_wait_bounded(bars.vec_full(j % NVEC), (j / NVEC) & 1, abort_flag, W_SM_VEC, kLimit))) break;
+      if (!WARP_ALL(mbar_wait_bounded(bars.qk_done(j % NK), (j / NK) & 1, abort_flag, W_SM_S, kLimit))) break;
       tc_fence_after();
       PK_STAMP(wg, j, 1);
       const uint32_t s_addr = lane_addr + C::COL_S + (j % NS) * kKeyTile;
@@ -432,12 +501,40 @@ fused_attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
       // Single pass over registers: the whole 64-column tile is loaded once, the score buffer is
       // re-armed and returned immediately, and t stays in registers between max and exp.
       uint32_t sraw[kKeyTile];
-      tmem_ld32(s_addr, sraw);
-      tmem_ld32(s_addr + 32, sraw + 32);
+      if (PK_ABL_SM < 2) {
+        tmem_ld32(s_addr, sraw);
+        tmem_ld32(s_addr + 32, sraw + 32);
+      } else {
+#pragma unroll
+        for (int i = 0; i < kKeyTile; ++i) sraw[i] = j + i;
+      }
       tmem_wait_ld();
       PK_STAMP(wg, j, 4);
+#if PK_SM_ARM_RELOAD
+      {
+        uint32_t arm_now[16];
+        load_arm_block(smem_base + C::OFF_MAGIC, arm_now);
 #pragma unroll
-      for (int c16 = 0; c16 < kKeyTile; c16 += 16) tmem_st16(s_addr + c16, armv);
+        for (int c16 = 0; c16 < kKeyTile; c16 += 16) tmem_st16(s_addr + c16, arm_now);
+      }
+#else
+      if (!PK_ABL_SMARM) {
+#pragma unroll
+        for (int c16 = 0; c16 < kKeyTile; c16 += 16) tmem_st16(s_addr + c16, armv);
+      }
+#endif
+#if PK_ABL_SM
+      const float bm = 0.f;
+      tmem_wait_st();
+      tc_fence_before();
+      mbar_arrive(bars.s_free(j % NS));
+      float ow = 1.f;
+      uint32_t packed[kKeyTile / 4];
+#pragma unroll
+      for (int c4 = 0; c4 < kKeyTile / 4; ++c4) packed[c4] = sraw[c4 * 4] & 0x01010101u;
+      float2 psum_a = make_float2(1.f, 0.f), psum_b = make_float2(0.f, 0.f);
+      (void)neg_magic2; (void)vk; (void)mt2; (void)diag; (void)lim; (void)m_run;
+#else
       float2 t2[kKeyTile / 2];
 #pragma unroll
       for (int ch = 0; ch < kKeyTile / 16; ++ch) scores16(sraw + ch * 16, ch, t2 + ch * 8);
@@ -458,7 +555,7 @@ fused_attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
         // memory; only this short hand-over is sequential, the exponentials of consecutive tiles
         // overlap.
         if (NSWG > 1 && j > 0) {
-          if (!WARP_ALL(mbar_wait_bounded(bars.m_ready((j - 1) % NM), ((j - 1) / NM) & 1, abort_flag, W_SM_M))) break;
+          if (!WARP_ALL(mbar_wait_bounded(bars.m_ready((j - 1) % NM), ((j - 1) / NM) & 1, abort_flag, W_SM_M, kLimit))) break;
           m_run = m_ring[((j - 1) % NM) * kQTile + row];
         }
         const float nm = fmaxf(m_run, bm);
@@ -496,13 +593,14 @@ fused_attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
           packed[c4] = __byte_perm(lo, hi, 0x5410);
         }
       }
+#endif
       PK_STAMP(wg, j, 5);
       // probability buffer j%NP was last read by the PV product of tile j-NP
-      if (j >= NP && !WARP_ALL(mbar_wait_bounded(bars.pv_done(j % NP), ((j / NP) - 1) & 1, abort_flag, W_SM_PV))) break;
+      if (j >= NP && !WARP_ALL(mbar_wait_bounded(bars.pv_done(j % NP), ((j / NP) - 1) & 1, abort_flag, W_SM_PV, kLimit))) break;
       tc_fence_after();
       PK_STAMP(wg, j, 6);
       const uint32_t p_addr = lane_addr + C::COL_P + (j % NP) * (kKeyTile / 4);
-      tmem_st16(p_addr, packed);
+      if (PK_ABL_SM < 2) tmem_st16(p_addr, packed);
       if (DUMP) {
         if (dumping && j == 0) {
           uint32_t* dp = reinterpret_cast<uint32_t*>(static_cast<char*>(prm.dump) + kQTile * kKeyTile * 4);
@@ -547,9 +645,11 @@ fused_attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
     float ow = 1.f, c = 0.f;      // factors of the tile being folded
     float ow_n = 1.f, c_n = 0.f;  // factors of the next tile
     auto advance_stats = [&](int j) -> bool {
-      if (!WARP_ALL(mbar_wait_bounded(bars.stat_full(j % NSTAT), (j / NSTAT) & 1, abort_flag, W_DQ_STAT))) return false;
+      if (!WARP_ALL(mbar_wait_bounded(bars.stat_full(j % NSTAT), (j / NSTAT) & 1, abort_flag, W_DQ_STAT, kLimit))) return false;
       const float2 st = stat_ring[(j % NSTAT) * kQTile + row];
-      if (ALGO == kPiper) {
+      if (PK_ABL_STATS) {
+        ow_n = 1.f; c_n = st.x; den += st.y;
+      } else if (ALGO == kPiper) {
         const float bm = st.x;
         const float nm = fmaxf(m, bm);
         float cw;
@@ -580,12 +680,16 @@ fused_attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
     load_arm_block(smem_base + C::OFF_MAGIC, armv);
     if (n_tiles > 0) {
       ok = advance_stats(0);
-      ok = ok && WARP_ALL(mbar_wait_bounded(bars.pv_done(0), 0, abort_flag, W_DQ_O));
+      ok = ok && WARP_ALL(mbar_wait_bounded(bars.pv_done(0), 0, abort_flag, W_DQ_O, kLimit));
       if (ok) {
         tc_fence_after();
-        tmem_ldN<CH>(lane_addr + C::COL_O + col0, obuf[0]);
+        if (PK_ABL_DQ < 2) tmem_ldN<CH>(lane_addr + C::COL_O + col0, obuf[0]);
       }
     }
+    constexpr bool BIAS = O_MAGIC && PK_DQ_BIAS_GROUP > 0;
+    constexpr bool LATE = PK_DQ_LATE_RELEASE != 0;
+    constexpr int NEXT_AT = (PK_DQ_NEXT_AT >= 0) ? ((PK_DQ_NEXT_AT < NCH - 1) ? PK_DQ_NEXT_AT : NCH - 2) : (LATE ? NCH - 2 : STAT_AT);  // chunk at which the next tile's product is waited for
+    float bias = 0.f;  // BIAS: what the folds since the last correction added to every column beyond the partials
     for (int j = 0; ok && j < n_tiles; ++j) {
       PK_STAMP(NSWG, j, 0);
       ow = ow_n; c = c_n;
@@ -594,7 +698,9 @@ fused_attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
         const float2 ow2 = make_float2(ow, ow);
 #pragma unroll
         for (int d = 0; d < DH / 2; ++d) num2[d] = __fmul2_rn(num2[d], ow2);
+        if (BIAS) bias = __fmul_rn(bias, ow);
       }
+      if (BIAS) bias = __fmaf_rn(kMagic, c, bias);  // the same operation every column's fold performs on 1.5*2^23
       const float2 c2 = make_float2(c, c);
       PK_STAMP(NSWG, j, 1);
 #pragma unroll
@@ -602,20 +708,28 @@ fused_attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
         tmem_wait_ld();
         if (ch == 0) PK_STAMP(NSWG, j, 2);
         if (ch + 1 < NCH) {
-          tmem_ldN<CH>(o_addr + (ch + 1) * CH, obuf[(ch + 1) & 1]);
+          if (PK_ABL_DQ < 2) tmem_ldN<CH>(o_addr + (ch + 1) * CH, obuf[(ch + 1) & 1]);
         } else if (j + 1 < n_tiles && ok) {
           // first chunk of the next tile (its product was waited for below, chunks ago)
-          tmem_ldN<CH>(lane_addr + C::COL_O + ((j + 1) % NO) * D + col0, obuf[(ch + 1) & 1]);
+          if (PK_ABL_DQ < 2) tmem_ldN<CH>(lane_addr + C::COL_O + ((j + 1) % NO) * D + col0, obuf[(ch + 1) & 1]);
         }
         if (ch == STAT_AT && j + 1 < n_tiles) {
           PK_STAMP(NSWG, j, 4);
           ok = advance_stats(j + 1);
           PK_STAMP(NSWG, j, 7);
-          ok = ok && WARP_ALL(mbar_wait_bounded(bars.pv_done((j + 1) % NP), ((j + 1) / NP) & 1, abort_flag, W_DQ_O));
+        }
+        if (LATE && ch == 1 && j > 0) {
+          // every arming store of tile j-1 was issued at least a chunk ago
+          if (O_MAGIC) tmem_wait_st();
+          tc_fence_before();
+          mbar_arrive(bars.o_empty((j - 1) % NO));
+        }
+        if (ch == NEXT_AT && j + 1 < n_tiles) {
+          ok = ok && WARP_ALL(mbar_wait_bounded(bars.pv_done((j + 1) % NP), ((j + 1) / NP) & 1, abort_flag, W_DQ_O, kLimit));
           tc_fence_after();
           PK_STAMP(NSWG, j, 5);
         }
-        if (O_MAGIC) {
+        if (O_MAGIC && !PK_ABL_DQARM) {
 #pragma unroll
           for (int c16 = 0; c16 < CH; c16 += 16) tmem_st16(o_addr + ch * CH + c16, armv);
         }
@@ -625,25 +739,47 @@ fused_attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
 #pragma unroll
           for (int i = 0; i < CH; ++i) dp[row * D + col0 + ch * CH + i] = O_MAGIC ? o[i] - kMagicBits : o[i];
         }
+#if PK_ABL_DQ
+        if (PK_ABL_DQ < 2 && o[0] == 0x12345u) num2[0].x += 1.f;
+#else
 #pragma unroll
         for (int i = 0; i < CH / 2; ++i) {
           float2 y = make_float2(__uint_as_float(o[2 * i]), __uint_as_float(o[2 * i + 1]));
           if (ALGO == kPiper) {
             // the word is the float 1.5*2^23 + partial; num += partial * c
-            num2[ch * (CH / 2) + i] = __ffma2_rn(__fadd2_rn(y, neg_magic2), c2, num2[ch * (CH / 2) + i]);
+            if (BIAS) num2[ch * (CH / 2) + i] = __ffma2_rn(y, c2, num2[ch * (CH / 2) + i]);
+            else num2[ch * (CH / 2) + i] = __ffma2_rn(__fadd2_rn(y, neg_magic2), c2, num2[ch * (CH / 2) + i]);
           } else {
             num2[ch * (CH / 2) + i] = __fadd2_rn(num2[ch * (CH / 2) + i], __half22float2(__floats2half2_rn(y.x, y.y)));
           }
         }
+#endif
       }
       PK_STAMP(NSWG, j, 6);
-      if (O_MAGIC) tmem_wait_st();
-      tc_fence_before();
-      mbar_arrive(bars.o_empty(j % NO));
+      if (!LATE || j + 1 == n_tiles) {
+        if (O_MAGIC) tmem_wait_st();
+        tc_fence_before();
+        mbar_arrive(bars.o_empty(j % NO));
+      }
+      if (BIAS && ((j + 1) % PK_DQ_BIAS_GROUP == 0 || j + 1 == n_tiles)) {
+        const float2 nb = make_float2(-bias, -bias);
+#pragma unroll
+        for (int d = 0; d < DH / 2; ++d) num2[d] = __fadd2_rn(num2[d], nb);
+        bias = 0.f;
+      }
       PK_STAMP(NSWG, j, 3);
     }
     // epilogue: normalise, restore the V mean (piper) / apply the channel scale (sage), cast
     const int grow = q0 + row;
+    if (!ok && grow < prm.Sq) {
+      // A wait was abandoned: this tile's rows are not valid.  They are filled with NaN so that a
+      // caller who never reads the status words cannot mistake them for results.
+      const long long obase = (static_cast<long long>(bh) * prm.Sq + grow) * D + col0;
+      for (int d0 = 0; d0 < DH; ++d0) {
+        if (prm.out_dtype == PK_F32) static_cast<float*>(prm.out)[obase + d0] = __int_as_float(0x7FC00000);
+        else static_cast<uint16_t*>(prm.out)[obase + d0] = (prm.out_dtype == PK_F16) ? 0x7E00 : 0x7FC0;
+      }
+    }
     if (ok && grow < prm.Sq) {
       // one IEEE division per row; the D per-element divisions of the reference become
       // multiplications by the reciprocal (at most an ulp apart, and far less code)
@@ -687,7 +823,10 @@ fused_attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
     tc_fence_after();
     tmem_dealloc(tmem_base, TMEM_COLS);
   }
-  if (tid == 0 && *abort_flag != 0) atomicCAS(prm.status, 0, *abort_flag);
+  if (tid == 0 && *abort_flag != 0) {
+    atomicCAS(prm.status, 0, *abort_flag);
+    if (prm.host_status != nullptr) atomicCAS_system(prm.host_status, 0, *abort_flag);
+  }
 }
 
 // ---------------------------------------------------------------------------------------
@@ -749,6 +888,8 @@ int launch_one_impl(const pk_problem& p, const Layout& L, cudaStream_t st, const
   prm.dump_qt = dump ? dump->q_tile : -1;
   prm.timeline = dump ? static_cast<long long*>(dump->timeline) : nullptr;
   prm.timeline_tiles = dump ? dump->timeline_tiles : 0;
+  prm.skip_key_tile = dump ? dump->skip_key_tile : -1;
+  prm.host_status = fault_word_device_ptr(p.device);
   auto kern = fused_attention_kernel<D, ALGO, KPB, CAUSAL, DEBUG>;
   {
     const cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES);
@@ -763,8 +904,11 @@ int launch_one_impl(const pk_problem& p, const Layout& L, cudaStream_t st, const
 
 template <int D, int ALGO, bool KPB>
 int launch_one(const pk_problem& p, const Layout& L, cudaStream_t st, const DebugDump* dump) {
+#ifndef PK_NO_DEBUG_KERNELS
   if (dump && dump->ptr) return launch_one_impl<D, ALGO, KPB, 2, 1>(p, L, st, dump);
   if (dump && dump->timeline) return launch_one_impl<D, ALGO, KPB, 2, 2>(p, L, st, dump);
+  if (dump && dump->skip_key_tile >= 0) return launch_one_impl<D, ALGO, KPB, 2, 3>(p, L, st, dump);
+#endif
   return p.is_causal ? launch_one_impl<D, ALGO, KPB, 1, 0>(p, L, st, dump) : launch_one_impl<D, ALGO, KPB, 0, 0>(p, L, st, dump);
 }
 

@@ -33,8 +33,11 @@ const char* cuda_err(cudaError_t e);
 // Argument checks shared by every entry point (does not touch the device).
 int validate(const pk_problem* p, Algo algo, bool need_workspace);
 
-// Prepass launchers (prepass.cu).  All asynchronous on `stream`.
-int launch_prepass(const pk_problem& p, const Layout& L, Algo algo, cudaStream_t stream);
+// Prepass launchers (prepass.cu).  All asynchronous on `stream`.  `parts` selects what is
+// quantised: the key/value side (statistics, key order, K and V codes, per-key vectors), the
+// query side (Q codes and row multipliers), or both.
+enum : int { kPrepassKV = 1, kPrepassQ = 2, kPrepassAll = 3 };
+int launch_prepass(const pk_problem& p, const Layout& L, Algo algo, cudaStream_t stream, int parts);
 
 // K and V sequence means with the partial sums in the library's own static device array
 // (prepass.cu).  The caller has validated `p` and made p.device current.
@@ -46,7 +49,14 @@ struct DebugDump {
   int bh, q_tile;   // which CTA
   void* timeline;   // per-role clock stamps (may be null)
   int timeline_tiles;
+  int skip_key_tile;  // >= 0: stalled-wait drill, the producer leaves out this key tile's copy
 };
+
+// Device-visible address of this device's fault word: one pinned, mapped host int that a fused
+// kernel writes its wait-site code to when it abandons a wait, so that the host can notice on its
+// next call without synchronising.  Created on first use per device (p.device current); nullptr
+// when the allocation is refused (the kernels then only write the workspace status words).
+int32_t* fault_word_device_ptr(int device);
 int launch_fused(const pk_problem& p, const Layout& L, Algo algo, cudaStream_t stream,
                  const DebugDump* dump);
 

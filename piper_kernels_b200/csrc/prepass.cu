@@ -18,6 +18,8 @@
 #include <cuda_fp8.h>
 #include <math.h>
 
+#include <atomic>
+
 #include "pk_internal.h"
 
 namespace pk {
@@ -537,7 +539,7 @@ bool aligned16(const void* ptr, const int64_t* s, int elem_bytes) {
 }
 
 template <typename T, int D, bool ALIGNED>
-int run_prepass(const pk_problem& p, const Layout& L, Algo algo, cudaStream_t st) {
+int run_prepass(const pk_problem& p, const Layout& L, Algo algo, cudaStream_t st, int parts) {
   const TensorArg q{p.q, p.q_stride[0], p.q_stride[1], p.q_stride[2]};
   const TensorArg k{p.k, p.k_stride[0], p.k_stride[1], p.k_stride[2]};
   const TensorArg v{p.v, p.v_stride[0], p.v_stride[1], p.v_stride[2]};
@@ -548,6 +550,18 @@ int run_prepass(const pk_problem& p, const Layout& L, Algo algo, cudaStream_t st
   const int per_thread = p.qk_granularity == PK_QK_PER_THREAD;
 
   zero_words_kernel<<<1, 32, 0, st>>>(at<int32_t>(p, L.status), 16);
+  const bool do_kv = (parts & kPrepassKV) != 0, do_q = (parts & kPrepassQ) != 0;
+
+  if (do_q) {
+    quantize_qk_kernel<T, D, false, ALIGNED><<<dim3(L.sq_pad / kBlockRows, BH), kThreads, 0, st>>>(
+        q, nullptr, nullptr, at<int8_t>(p, L.q_codes), at<float>(p, L.q_gscale), at<float>(p, L.q_mul), L.Sq,
+        L.sq_pad, p.heads, per_thread, L.q_groups, p.scale * kLog2e);
+  }
+  if (!do_kv) {
+    const cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) return fail(PK_ERR_CUDA, "prepass launch failed: %s", cuda_err(e));
+    return PK_OK;
+  }
 
   // 1. column statistics
   const int do_k = p.k_mean_override == nullptr;
@@ -574,11 +588,7 @@ int run_prepass(const pk_problem& p, const Layout& L, Algo algo, cudaStream_t st
     order = at<int32_t>(p, L.idx_a);
   }
 
-  // 3. Q, K codes
-  const float qmul = p.scale * kLog2e;
-  quantize_qk_kernel<T, D, false, ALIGNED><<<dim3(L.sq_pad / kBlockRows, BH), kThreads, 0, st>>>(
-      q, nullptr, nullptr, at<int8_t>(p, L.q_codes), at<float>(p, L.q_gscale), at<float>(p, L.q_mul), L.Sq,
-      L.sq_pad, p.heads, per_thread, L.q_groups, qmul);
+  // 3. K codes
   quantize_qk_kernel<T, D, true, ALIGNED><<<dim3(L.sk_pad / kBlockRows, BH), kThreads, 0, st>>>(
       k, at<float>(p, L.k_mean), order, at<int8_t>(p, L.k_codes), at<float>(p, L.k_gscale), at<float>(p, L.k_mul),
       L.Sk, L.sk_pad, p.heads, per_thread, L.k_groups, 1.0f);
@@ -599,20 +609,22 @@ int run_prepass(const pk_problem& p, const Layout& L, Algo algo, cudaStream_t st
 }
 
 template <typename T, int D>
-int run_prepass_a(const pk_problem& p, const Layout& L, Algo algo, cudaStream_t st) {
+int run_prepass_a(const pk_problem& p, const Layout& L, Algo algo, cudaStream_t st, int parts) {
   const int eb = 2;
-  const bool al = aligned16(p.q, p.q_stride, eb) && aligned16(p.k, p.k_stride, eb) && aligned16(p.v, p.v_stride, eb);
-  return al ? run_prepass<T, D, true>(p, L, algo, st) : run_prepass<T, D, false>(p, L, algo, st);
+  // only the tensors this call reads decide between vector and element-wise loads
+  const bool al = (!(parts & kPrepassQ) || aligned16(p.q, p.q_stride, eb)) &&
+                  (!(parts & kPrepassKV) || (aligned16(p.k, p.k_stride, eb) && aligned16(p.v, p.v_stride, eb)));
+  return al ? run_prepass<T, D, true>(p, L, algo, st, parts) : run_prepass<T, D, false>(p, L, algo, st, parts);
 }
 
 }  // namespace
 
-int launch_prepass(const pk_problem& p, const Layout& L, Algo algo, cudaStream_t st) {
+int launch_prepass(const pk_problem& p, const Layout& L, Algo algo, cudaStream_t st, int parts) {
   if (p.in_dtype == PK_F16) {
-    return p.head_dim == 128 ? run_prepass_a<__half, 128>(p, L, algo, st) : run_prepass_a<__half, 64>(p, L, algo, st);
+    return p.head_dim == 128 ? run_prepass_a<__half, 128>(p, L, algo, st, parts) : run_prepass_a<__half, 64>(p, L, algo, st, parts);
   }
-  return p.head_dim == 128 ? run_prepass_a<__nv_bfloat16, 128>(p, L, algo, st)
-                           : run_prepass_a<__nv_bfloat16, 64>(p, L, algo, st);
+  return p.head_dim == 128 ? run_prepass_a<__nv_bfloat16, 128>(p, L, algo, st, parts)
+                           : run_prepass_a<__nv_bfloat16, 64>(p, L, algo, st, parts);
 }
 
 // ---------------------------------------------------------------------------------------
@@ -633,15 +645,18 @@ static __device__ __align__(256) double g_static_mean_partials[2 * kStaticPartia
 // Device address of the array, looked up once per device while that device is current.  The
 // array's name in host code is only a handle for this lookup, never a pointer to pass along.
 double* static_partials_for_current_device(int device, cudaError_t* err) {
-  static double* cache[64] = {};
-  if (device >= 0 && device < 64 && cache[device] != nullptr) {
-    *err = cudaSuccess;
-    return cache[device];
+  // Threads that make the first call on a device at the same time all look the address up and
+  // store the same value; later calls read it without touching the runtime.
+  static std::atomic<double*> cache[64];
+  *err = cudaSuccess;
+  if (device >= 0 && device < 64) {
+    double* known = cache[device].load(std::memory_order_acquire);
+    if (known != nullptr) return known;
   }
   double* ptr = nullptr;
   *err = cudaGetSymbolAddress(reinterpret_cast<void**>(&ptr), g_static_mean_partials);
   if (*err != cudaSuccess) return nullptr;
-  if (device >= 0 && device < 64) cache[device] = ptr;
+  if (device >= 0 && device < 64) cache[device].store(ptr, std::memory_order_release);
   return ptr;
 }
 

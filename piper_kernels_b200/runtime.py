@@ -52,6 +52,31 @@ class AttentionCall:
         _cabi.check(self._fn("prepare")(C.byref(self.p), C.byref(self.views)))
         return self
 
+    def prepare_kv(self):
+        """Key/value side of the prepass only (means, key order, K and V codes, per-key vectors)."""
+        self._sync_stream()
+        _cabi.check(self._fn("prepare_kv")(C.byref(self.p), C.byref(self.views)))
+        return self
+
+    def requantize_q(self, new_q=None):
+        """Query side of the prepass only, on this call's workspace.  ``new_q`` (same shape and
+        dtype as the original query, any strides) replaces the query; K/V stay as prepared."""
+        if new_q is not None:
+            if new_q.shape != self.q.shape or new_q.dtype != self.q.dtype or new_q.device != self.q.device:
+                raise ValueError("requantize_q needs a query of the prepared shape, dtype and device")
+            self.q = new_q
+            self.p.q = new_q.data_ptr()
+            self.p.q_stride = (C.c_int64 * 3)(new_q.stride(0), new_q.stride(1), new_q.stride(2))
+        self._sync_stream()
+        _cabi.check(self._fn("prepare_q")(C.byref(self.p), C.byref(self.views)))
+        return self
+
+    def stalled_wait_drill(self, skip_key_tile: int = 1):
+        """pk_debug_stalled_wait on the prepared workspace (see include/piper_b200.h)."""
+        self._sync_stream()
+        _cabi.check(self.lib.pk_debug_stalled_wait(C.byref(self.p), int(self.algo != "piper"), int(skip_key_tile)))
+        return self
+
     def run(self):
         """Fused kernel only, on the prepared workspace."""
         self._sync_stream()

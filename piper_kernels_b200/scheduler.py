@@ -137,7 +137,10 @@ class HostAttentionPipeline:
             self._calls[key] = call
         return call
 
-    def __call__(self, op, q_host, k_host, v_host, out_host, **kwargs) -> torch.Tensor:
+    def __call__(self, op, q_host, k_host, v_host, out_host, *, copy_only: bool = False, **kwargs) -> torch.Tensor:
+        """``copy_only=True`` performs the same uploads and downloads in the same order and with the
+        same stream dependencies but launches no kernel: the time the host link alone needs (a
+        measurement aid; ``out_host`` then receives whatever the staging outputs hold)."""
         b, h = q_host.shape[:2]
         flat = b * h
         fq, fk, fv = (t.flatten(0, 1) for t in (q_host, k_host, v_host))
@@ -162,13 +165,15 @@ class HostAttentionPipeline:
                 uploaded.record(self.up)
             with torch.cuda.stream(self.prep):
                 self.prep.wait_event(uploaded)
-                call.prepare()
+                if not copy_only:
+                    call.prepare()
                 prepared = torch.cuda.Event()
                 prepared.record(self.prep)
             main.wait_event(prepared)
             if call.drained is not None:
                 main.wait_event(call.drained)  # the download of this call's previous result has finished
-            call.run()
+            if not copy_only:
+                call.run()
             slot["free"] = torch.cuda.Event()
             slot["free"].record(main)
             with torch.cuda.stream(self.down):

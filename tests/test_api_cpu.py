@@ -129,6 +129,24 @@ def test_abi_argument_errors_without_gpu():
     assert b"too small" in lib.pk_last_error()
 
 
+def test_abi_rejects_more_flat_heads_than_a_grid_dimension_holds():
+    lib = _cabi.lib()
+    n = C.c_uint64()
+    assert lib.pk_piper_workspace_bytes(C.byref(_problem(batch=65535, heads=1, q_len=8, kv_len=8)), C.byref(n)) == _cabi.PK_OK
+    assert lib.pk_piper_workspace_bytes(C.byref(_problem(batch=256, heads=256, q_len=8, kv_len=8)), C.byref(n)) == _cabi.PK_ERR_BAD_ARG
+    assert b"65535" in lib.pk_last_error()
+
+
+def test_fault_poll_reports_nothing_before_any_launch_and_maps_errors():
+    lib = _cabi.lib()
+    code = C.c_int32(7)
+    assert lib.pk_poll_device_fault(0, C.byref(code)) == _cabi.PK_OK and code.value == 0
+    assert lib.pk_poll_device_fault(-1, C.byref(code)) == _cabi.PK_ERR_BAD_ARG
+    with pytest.raises(_cabi.PiperB200Error) as exc:
+        _cabi.check(lib.pk_poll_device_fault(1000, C.byref(code)))
+    assert exc.value.code == _cabi.PK_ERR_BAD_ARG
+
+
 def test_workspace_grows_with_sorting_and_granularity():
     lib = _cabi.lib()
     a, b = C.c_uint64(), C.c_uint64()

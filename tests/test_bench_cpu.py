@@ -21,5 +21,8 @@ def test_reference_arm_prints_one_json_line_with_the_contract_keys():
     assert d["value"] > 0 and d["ms_per_step"] > 0
     assert d["config"]["workload"].startswith("c1")
     cb = d["cpu_baseline"]
-    assert cb["kind"] == "port" and cb["cores"] >= 1 and cb["value"] == d["value"] and cb["sample"]
+    # the reference's own torch loop when it is installed beside the oracle, else the numpy port
+    installed = (ROOT / "oracle" / "_ref" / "piper_kernels" / "attention" / "piper" / "reference.py").exists()
+    assert cb["kind"] == ("reference" if installed else "port")
+    assert cb["cores"] >= 1 and cb["value"] == d["value"] and cb["sample"]
     assert d["e2e"] == {"value": d["value"], "unit": "TOPS", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}

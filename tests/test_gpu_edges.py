@@ -23,6 +23,29 @@ def _rand(shape, dtype, seed, scale=1.0, shift=0.0):
     return (torch.randn(shape, generator=g) * scale + shift).to(dtype).cuda()
 
 
+MAX_ABS = 2e-3  # on FP32 outputs, no allowance for the output type
+MIN_COS = 0.9999
+
+
+def _out32(algo, q, k, v, scale, causal, **kw):
+    from piper_kernels_b200.runtime import AttentionCall
+
+    call = AttentionCall(algo, q, k, v, scale, causal, out_dtype=torch.float32, **kw).fwd()
+    assert call.status()[0] == 0
+    return _np(call.out)
+
+
+def _ulp16(x, dtype):
+    frac = 10 if dtype == torch.float16 else 7
+    e = np.floor(np.log2(np.maximum(np.abs(x), 2.0 ** -14)))
+    return 2.0 ** (e - frac)
+
+
+def _check16(out16, out32, dtype):
+    """The public operator's 16-bit output is the FP32 output rounded once."""
+    assert np.array_equal(out16, oracle.round_to_dtype(out32, "f16" if dtype == torch.float16 else "bf16"))
+
+
 @pytest.mark.parametrize("sq,sk", [(1, 1), (1, 17), (17, 1), (63, 64), (64, 65), (65, 63), (128, 128), (129, 257), (257, 129)])
 @pytest.mark.parametrize("d", [64, 128])
 def test_ragged_lengths_piper_and_sage(sq, sk, d):
@@ -30,58 +53,75 @@ def test_ragged_lengths_piper_and_sage(sq, sk, d):
     k = _rand((1, 2, sk, d), torch.float16, 200 + sk, shift=0.25)
     v = _rand((1, 2, sk, d), torch.float16, 300 + sk)
     for center in (False, True):
-        out = _np(pk.piper_attention(q, k, v, center_value=center))
+        out = _out32("piper", q, k, v, d ** -0.5, False, center=center)
         want = oracle.piper_attention_oracle(_np(q), _np(k), _np(v), d ** -0.5, False, center_value=center,
                                              qk_quantization="per_warp")
         assert np.isfinite(out).all()
-        assert np.all(np.abs(out - want) <= 2e-3 + np.abs(want) * 2.0 ** -10)
-    out = _np(pk.sage_attention_2pp(q, k, v))
+        assert np.abs(out - want).max() <= MAX_ABS
+        _check16(_np(pk.piper_attention(q, k, v, center_value=center)), out, torch.float16)
+    out = _out32("sage2pp", q, k, v, d ** -0.5, False)
     want = oracle.sage_attention_2pp_oracle(_np(q), _np(k), _np(v), d ** -0.5, False, qk_quantization="per_thread")
-    assert np.all(np.abs(out - want) <= 2e-3 + np.abs(want) * 2.0 ** -10)
+    assert np.abs(out - want).max() <= MAX_ABS
+    _check16(_np(pk.sage_attention_2pp(q, k, v)), out, torch.float16)
 
 
-@pytest.mark.parametrize("s", [1, 64, 100, 257])
+@pytest.mark.parametrize("s", [1, 64, 100, 257, 1000])
 def test_causal_lengths(s):
     q = _rand((2, 1, s, 128), torch.bfloat16, 400 + s)
     k = _rand((2, 1, s, 128), torch.bfloat16, 500 + s)
     v = _rand((2, 1, s, 128), torch.bfloat16, 600 + s)
-    out = _np(pk.piper_attention(q, k, v, is_causal=True))
+    out = _out32("piper", q, k, v, 128 ** -0.5, True)
     want = oracle.piper_attention_oracle(_np(q), _np(k), _np(v), 128 ** -0.5, True, center_value=False,
                                          qk_quantization="per_warp")
-    assert np.all(np.abs(out - want) <= 2e-3 + np.abs(want) * 2.0 ** -7)
-    out = _np(pk.sage_attention_2pp(q, k, v, is_causal=True))
+    assert np.abs(out - want).max() <= MAX_ABS and cosine(out, want) >= MIN_COS
+    _check16(_np(pk.piper_attention(q, k, v, is_causal=True)), out, torch.bfloat16)
+    out = _out32("sage2pp", q, k, v, 128 ** -0.5, True)
     want = oracle.sage_attention_2pp_oracle(_np(q), _np(k), _np(v), 128 ** -0.5, True, qk_quantization="per_thread")
-    assert np.all(np.abs(out - want) <= 2e-3 + np.abs(want) * 2.0 ** -7)
+    assert np.abs(out - want).max() <= MAX_ABS and cosine(out, want) >= MIN_COS
+    _check16(_np(pk.sage_attention_2pp(q, k, v, is_causal=True)), out, torch.bfloat16)
 
 
 def test_many_small_heads_and_custom_scale():
+    """128 heads of 72 keys with a sharp softmax (scale 0.2).  Here one probability code is worth
+    up to 1/255 of a value: in a row that two or three keys dominate, a code that rounds the other
+    way moves the output by up to max|v - mean| / 255 (about 1.6e-2 for these values).  The
+    kernel evaluates 2^(t - max t) with the key scale folded into one multiplier, the reference
+    exp(s - max) * vscale * 255 in its own operation order; both are within a few 1e-6 of the
+    exact exponent, so about one code in a thousand lands on the other side of a rounding
+    boundary.  With thousands of keys such a step is invisible; with 72 it is the tail measured
+    here.  Asserted: the bulk at the 1e-5 level, fewer than one element in ten thousand beyond
+    2e-3, and no element beyond the value of one code step."""
     q = _rand((8, 16, 40, 64), torch.float16, 7)
     k = _rand((8, 16, 72, 64), torch.float16, 8)
     v = _rand((8, 16, 72, 64), torch.float16, 9)
-    out = _np(pk.piper_attention(q, k, v, scale=0.2, center_value=True))
+    out = _out32("piper", q, k, v, 0.2, False, center=True)
     want = oracle.piper_attention_oracle(_np(q), _np(k), _np(v), 0.2, False, center_value=True, qk_quantization="per_warp")
-    # With 72 keys and a sharp softmax a single probability code that rounds the other way
-    # (the CUDA path works in base 2, the oracle in base e: ~1e-3 of the codes differ by one
-    # step) moves one output row by up to ~1/255 of a value; the bulk stays at ~3e-5.
     diff = np.abs(out - want)
+    vf = _np(v)
+    code_step = float(np.abs(vf - vf.mean(axis=2, keepdims=True)).max()) / 255.0
+    print(f"sharp 72-key rows: mean {diff.mean():.2e}, max {diff.max():.2e}, beyond 2e-3: {(diff > MAX_ABS).mean():.2e}, "
+          f"one code step {code_step:.2e}")
     assert diff.mean() <= 1e-4
-    assert (diff > 2e-3 + np.abs(want) * 2.0 ** -10).mean() < 1e-4
-    assert diff.max() <= 6e-3
-    assert cosine(out, want) >= 0.9999
+    assert (diff > MAX_ABS).mean() < 1e-4
+    assert diff.max() <= code_step
+    assert cosine(out, want) >= MIN_COS
 
 
 def test_large_magnitudes_and_zero_rows():
+    """Inputs far from unit scale (values x50, keys shifted by 30): the gate scales with the
+    output magnitude, as the reference's own large-value test does."""
     q = _rand((1, 2, 150, 128), torch.bfloat16, 21, scale=8.0)
     k = _rand((1, 2, 190, 128), torch.bfloat16, 22, scale=8.0, shift=30.0)
     v = _rand((1, 2, 190, 128), torch.bfloat16, 23, scale=50.0)
     v[:, :, 5] = 0  # an all-zero value row (scale = epsilon)
     q[:, :, 3] = 0  # an all-zero query row (uniform attention)
-    out = _np(pk.piper_attention(q, k, v, center_value=False))
+    out = _out32("piper", q, k, v, 128 ** -0.5, False, center=False)
     want = oracle.piper_attention_oracle(_np(q), _np(k), _np(v), 128 ** -0.5, False, center_value=False,
                                          qk_quantization="per_warp")
     assert np.isfinite(out).all()
     mag = float(np.abs(want).max())
-    assert np.all(np.abs(out - want) <= 2e-3 * mag + np.abs(want) * 2.0 ** -7)
+    assert np.abs(out - want).max() <= MAX_ABS * mag
+    assert cosine(out, want) >= MIN_COS
 
 
 def test_abi_rejects_bad_arguments_on_device():
@@ -112,3 +152,53 @@ def test_status_words_are_clean_after_runs():
     assert call.status() == [0] * 16
     call = AttentionCall("sage2pp", q, q, q, 128 ** -0.5, False).fwd()
     assert call.status() == [0] * 16
+
+
+def test_prepared_kv_reused_for_three_query_batches_equals_three_full_calls():
+    """K/V quantised once (pk_*_prepare_kv), then three different query batches through
+    pk_*_prepare_q + pk_*_run: each result equals a full call on the same inputs bit for bit."""
+    from piper_kernels_b200.runtime import AttentionCall
+
+    k = _rand((2, 3, 1200, 128), torch.bfloat16, 41, shift=0.5)
+    v = _rand((2, 3, 1200, 128), torch.bfloat16, 42, shift=1.5)
+    qs = [_rand((2, 3, 300, 128), torch.bfloat16, 50 + i) for i in range(3)]
+    qs[1] = _rand((3, 2, 300, 128), torch.bfloat16, 60).permute(1, 0, 2, 3)  # other strides, same shape
+    for algo, kw in (("piper", dict(center=True)), ("sage2pp", {})):
+        call = AttentionCall(algo, qs[0], k, v, 128 ** -0.5, False, **kw).prepare_kv()
+        for q in qs:
+            got = call.requantize_q(q).run().out.clone()
+            want = AttentionCall(algo, q, k, v, 128 ** -0.5, False, **kw).fwd().out
+            assert torch.equal(got, want)
+        assert call.status()[0] == 0
+
+
+def test_stalled_wait_gives_up_reports_and_leaves_the_device_usable():
+    """The failure path of the fused kernel, exercised without faulting anything: the drill
+    instantiation leaves out one K tile's copy and limits every wait to ~0.1 ms.  The wait for the
+    missing tile expires, all roles unwind and the kernel returns; the status word and the pinned
+    fault word name the wait site, the rows are NaN, the next public call raises once, and an
+    ordinary call on the same device then works and is exact."""
+    from piper_kernels_b200 import _cabi, _ops
+    from piper_kernels_b200.runtime import AttentionCall
+
+    q = _rand((1, 2, 256, 128), torch.float16, 71)
+    k = _rand((1, 2, 512, 128), torch.float16, 72)
+    v = _rand((1, 2, 512, 128), torch.float16, 73)
+    good = AttentionCall("piper", q, k, v, 128 ** -0.5, False).fwd()
+    assert good.status()[0] == 0
+    want = good.out.clone()
+    _ops.poll_device_fault(0)  # clean so far
+
+    call = AttentionCall("piper", q, k, v, 128 ** -0.5, False).prepare()
+    call.stalled_wait_drill(skip_key_tile=2)
+    st = (C.c_int32 * 16)()
+    rc = _cabi.lib().pk_device_status(C.byref(call.p), C.byref(st))
+    assert rc == _cabi.PK_ERR_DEVICE_STATUS and st[0] == 22  # S-product issue warp waiting for a K tile
+    assert torch.isnan(call.out).all()
+    with pytest.raises(_cabi.PiperB200Error) as exc:
+        pk.piper_attention(q, k, v)  # the public operator notices at its next call, without a sync
+    assert exc.value.code == _cabi.PK_ERR_DEVICE_STATUS
+    again = pk.piper_attention(q, k, v, center_value=False)  # reported once; the device is healthy
+    torch.cuda.synchronize()
+    assert torch.equal(again, want)
+    assert AttentionCall("sage2pp", q, k, v, 128 ** -0.5, False).fwd().status()[0] == 0

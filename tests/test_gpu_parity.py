@@ -124,6 +124,39 @@ def test_piper_first_tile_integer_products_exact(name):
     assert (diff > 0).mean() < 0.01
 
 
+@pytest.mark.parametrize("name", ["sage_d64_s193_f16", "sage_d128_sk17_offset_bf16"])
+def test_sage_first_tile_products(name):
+    """First key tile of one query tile from tensor memory: S = Q8 K8^T exact; the E4M3 probability
+    codes equal e4m3(448 * 2^(t - max t)) up to one code step in rare elements; the FP32 partial
+    equals the product of the decoded codes with the decoded E4M3 values."""
+    from _gpu import Call
+    g = load_golden(name)
+    q, k, v = _inputs(g)
+    call = Call("sage2pp", q, k, v, g["scale"], False, gran="per_thread", out_dtype=torch.float32).prepare()
+    s, pc, o = call.debug_tile(bh=1, q_tile=0)
+    assert call.status()[0] == 0
+    o = o.view(np.float32)
+    prep = oracle.sage_prepare_oracle(g["qf"], g["kf"], g["vf"], qk_quantization="per_thread")
+    q8 = _flat(prep["q_codes"])[1].astype(np.int32)
+    k8 = _flat(prep["k_codes"])[1].astype(np.int32)
+    v8 = oracle.e4m3_decode(_flat(prep["v_codes"])[1]).astype(np.float64)
+    rows, keys = min(128, q8.shape[0]), min(64, k8.shape[0])
+    want_s = q8[:rows] @ k8[:keys].T
+    assert np.array_equal(s[:rows, :keys], want_s)
+    qs = _flat(prep["q_scale"])[1][:rows, None].astype(np.float64)
+    ks = _flat(prep["k_scale"])[1][None, :keys].astype(np.float64)
+    t = want_s * qs * ks * g["scale"] * np.log2(np.e)
+    e = np.exp2(t - t.max(axis=1, keepdims=True))
+    want_codes = oracle.e4m3_encode((448.0 * e).astype(np.float32))
+    got = pc[:rows, :keys]
+    step = np.abs(got.astype(np.int32) - want_codes.astype(np.int32))
+    assert step.max() <= 1 and (step > 0).mean() < 0.01
+    assert not pc[:rows, keys:].any()  # masked padding keys carry probability zero
+    p_dec = oracle.e4m3_decode(got).astype(np.float64)
+    want_o = p_dec @ v8[:keys]
+    assert np.abs(o[:rows] - want_o).max() <= 2.0 ** -12 * max(1.0, float(np.abs(want_o).max()))
+
+
 def _gpu_out(algo, g, gran, out_dtype, **kw):
     from _gpu import Call, f32
     q, k, v = _inputs(g)
@@ -146,12 +179,14 @@ def test_piper_output_vs_oracle_and_reference(name, gran):
     out, _ = _gpu_out("piper", g, gran, torch.float32, center=g["center"], sort=g["sort"])
     want = oracle.piper_attention_oracle(g["qf"], g["kf"], g["vf"], g["scale"], g["causal"], center_value=g["center"],
                                          qk_quantization=gran, sort_value_rows=g["sort"])
-    mag = max(1.0, float(np.abs(want).max()))
+    # Absolute gate on FP32 outputs.  The one fixture whose values reach 40000 keeps the bound the
+    # reference's own test uses for it (2^-9 of the largest output, tests/attention/piper/test_triton.py:118-147).
+    gate = 2.0 ** -9 * float(np.abs(want).max()) if name == "piper_d128_huge_v" else MAX_ABS
     assert np.isfinite(out).all()
-    assert np.abs(out - want).max() <= MAX_ABS * mag
+    assert np.abs(out - want).max() <= gate
     assert cosine(out, want) >= MIN_COS
     ref = g[f"out32_{gran}"]  # the reference's own FP32 output (its torch means)
-    assert np.abs(out - ref).max() <= MAX_ABS * mag
+    assert np.abs(out - ref).max() <= gate
     assert cosine(out, ref) >= MIN_COS
 
 
