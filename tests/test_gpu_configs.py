@@ -2,8 +2,8 @@
 
 The gate is the one stated for the path: un-rounded FP32 output of the CUDA kernels against the
 FP32 oracle, max-abs <= 2e-3 and cosine >= 0.9999, with no allowance for the output type.  The
-16-bit output of the public operator is checked separately: it is the rounded FP32 output, and
-it lies within one unit in the last place of the rounded oracle.  Whole tensors or whole heads
+16-bit output of the public operator is checked separately: it is the FP32 output rounded once
+to the output type.  Whole tensors or whole heads
 are compared where the oracle finishes in seconds (c1, a c2 head, a c5 head); for c3 and c4 one
 head runs on the GPU at full length and several row blocks spread over the sequence are
 compared (rows are independent given the head's K/V).  Size-independent properties
@@ -48,10 +48,12 @@ def _gate32(out32, want32):
 
 
 def _gate16(out16, out32, want32, dtype):
-    """The 16-bit output is the rounded FP32 output, one ulp at most from the rounded oracle."""
+    """The 16-bit output of the public operator is the FP32 output rounded once (so the only
+    difference between the two outputs is the output type's own rounding), and it lies within
+    the gate plus one unit in the last place of the rounded oracle."""
     assert np.array_equal(out16, oracle.round_to_dtype(out32, SHORT[dtype]))
     want16 = oracle.round_to_dtype(want32, SHORT[dtype])
-    assert np.all(np.abs(out16 - want16) <= _ulp16(want16, dtype))
+    assert np.all(np.abs(out16 - want16) <= MAX_ABS + _ulp16(want16, dtype))
 
 
 def _policy(w, q, k):
