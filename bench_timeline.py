@@ -1,6 +1,7 @@
-"""Per-role timeline of one CTA of the fused kernel (profiling aid).
+#!/usr/bin/env python
+"""Per-role timeline of one CTA of the fused kernel (profiling aid, beside bench.py).
 
-    python -m piper_kernels_b200.timeline [--workload c2] [--bh 5] [--q-tile 7]
+    python bench_timeline.py [--workload c2] [--bh 5] [--q-tile 7]
 
 Runs the ordinary fused kernel through ``pk_debug_timeline`` and prints, per warp role, the
 average cycles per key tile spent waiting and working, plus the steady-state tile period.
@@ -14,10 +15,15 @@ import ctypes as C
 import numpy as np
 import torch
 
-from . import _cabi
-from .attention.piper import default_center_value, should_sort_value_rows
-from .runtime import AttentionCall
-from .workloads import WORKLOADS, make_inputs
+import sys
+from pathlib import Path
+
+sys.path.insert(0, str(Path(__file__).resolve().parent))
+
+from piper_kernels_b200 import _cabi  # noqa: E402
+from piper_kernels_b200.attention.piper import default_center_value, should_sort_value_rows  # noqa: E402
+from piper_kernels_b200.runtime import AttentionCall  # noqa: E402
+from piper_kernels_b200.workloads import WORKLOADS, make_inputs  # noqa: E402
 
 ROLES = 7
 
@@ -36,7 +42,7 @@ def summarize(tr: np.ndarray, n_tiles: int, nswg: int) -> str:
     6 probability buffer free, 7 probabilities stored, 3 published; dequant 0 start, 1 rescaled,
     2 first chunk loaded, 4 early chunks folded, 7 next statistics done, 5 next tile's product
     complete, 6 all chunks folded, 3 buffer released; issue warps 0 start, 1 operands
-    ready, 2 issued."""
+    ready, 2 issued; producer 0 start, 1 K stage free, 2 copies issued."""
     n = min(n_tiles, tr.shape[1])
     t0 = tr[tr > 0].min()
     tr = np.where(tr > 0, tr - t0, -1)[:, :n]
@@ -58,6 +64,9 @@ def summarize(tr: np.ndarray, n_tiles: int, nswg: int) -> str:
     for r, name in ((nswg + 1, "S issue "), (nswg + 2, "PV issue")):
         x = tr[r, lo:hi]
         lines.append(f"{name}: wait {d(x, 0, 1):.0f} | issue {d(x, 1, 2):.0f} | per tile {np.mean(np.diff(x[:, 0])):.0f}")
+    x = tr[nswg + 3, lo:hi]
+    if x[:, 2].min() >= 0:
+        lines.append(f"producer: wait K stage {d(x, 0, 1):.0f} | wait V stage + issue copies {d(x, 1, 2):.0f} | per tile {np.mean(np.diff(x[:, 0])):.0f}")
     own = np.arange(n) % nswg
     p_done = tr[own, np.arange(n), 3]
     lines.append(f"P published -> PV issued {np.mean(tr[nswg + 2, lo:hi, 2] - p_done[lo:hi]):.0f} | PV issued -> fold begins {np.mean(tr[nswg, lo:hi, 0] - tr[nswg + 2, lo:hi, 2]):.0f} | "

@@ -46,6 +46,7 @@ __device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
   asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes)
                : "memory");
 }
+// One potentially blocking probe of a phase.
 __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
   uint32_t ok;
   asm volatile(
@@ -58,62 +59,29 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
   return ok != 0;
 }
 
-// Non-blocking probe of a phase (used where one thread polls several barriers).
-__device__ __forceinline__ bool mbar_test_wait(uint32_t bar, uint32_t parity) {
-  uint32_t ok;
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-      "selp.u32 %0, 1, 0, p;\n\t}"
-      : "=r"(ok)
-      : "r"(bar), "r"(parity)
-      : "memory");
-  return ok != 0;
-}
-
 // Wait limit: ~1.5e9 SM cycles (well under a second at any clock this part runs at).
 constexpr long long kWaitCycleLimit = 1500000000LL;
 
-// Time limit, in nanoseconds, that a failed mbarrier.try_wait may keep its thread suspended before
-// it returns "not yet".  Without the operand the limit is short and a waiting lane comes back
-// every few dozen cycles; each return costs the loop's instructions in issue slots that the
-// compute warps of the same scheduler need.  A thread suspended in try_wait resumes as soon as
-// the phase completes, so a long limit adds no latency.
-#ifndef PK_TRYWAIT_HINT_NS
-#define PK_TRYWAIT_HINT_NS 0
-#endif
-
-// One potentially blocking probe of a phase.
-__device__ __forceinline__ bool mbar_try_wait_hint(uint32_t bar, uint32_t parity) {
-  uint32_t ok;
-#if PK_TRYWAIT_HINT_NS > 0
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
-      "selp.u32 %0, 1, 0, p;\n\t}"
-      : "=r"(ok)
-      : "r"(bar), "r"(parity), "r"(static_cast<uint32_t>(PK_TRYWAIT_HINT_NS))
-      : "memory");
-#else
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-      "selp.u32 %0, 1, 0, p;\n\t}"
-      : "=r"(ok)
-      : "r"(bar), "r"(parity)
-      : "memory");
-#endif
-  return ok != 0;
-}
-
 // Slow path of a wait (inlined: an out-of-line call cannot be shared by roles that run with
-// different register allocations).  After every probe that came back empty the abort flag and
-// the clock are checked.
+// different register allocations).  The probe loop is written in PTX so that one iteration is a
+// handful of instructions: the warps that spin here (producer, issue warps) share their
+// scheduler with the compute warps.  Every 64 probes the abort flag and the clock are checked.
 __device__ __forceinline__ bool mbar_wait_slow(uint32_t bar, uint32_t parity, volatile int* abort_flag,
                                             int where, long long limit) {
   const long long t0 = clock64();
   while (true) {
-    if (mbar_try_wait_hint(bar, parity)) return true;
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p, q;\n\t.reg .u32 n;\n\tmov.u32 n, 64;\n"
+        "PK_WAIT_PROBE:\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "@p bra PK_WAIT_DONE;\n\t"
+        "sub.u32 n, n, 1;\n\tsetp.ne.u32 q, n, 0;\n\t@q bra PK_WAIT_PROBE;\n"
+        "PK_WAIT_DONE:\n\tselp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    if (ok) return true;
     if (*abort_flag != 0) return false;
     if (clock64() - t0 > limit) {
       *abort_flag = where;
@@ -127,7 +95,7 @@ __device__ __forceinline__ bool mbar_wait_slow(uint32_t bar, uint32_t parity, vo
 __device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity,
                                                   volatile int* abort_flag, int where,
                                                   long long limit = kWaitCycleLimit) {
-  if (mbar_try_wait_hint(bar, parity)) return true;
+  if (mbar_try_wait(bar, parity)) return true;
   return mbar_wait_slow(bar, parity, abort_flag, where, limit);
 }
 
@@ -135,7 +103,7 @@ __device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity,
 // that are still in flight land before a CTA that is giving up returns).
 __device__ __forceinline__ void mbar_wait_quiet(uint32_t bar, uint32_t parity, long long limit) {
   const long long t0 = clock64();
-  while (!mbar_try_wait_hint(bar, parity) && clock64() - t0 <= limit) {
+  while (!mbar_try_wait(bar, parity) && clock64() - t0 <= limit) {
   }
 }
 
