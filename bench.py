@@ -43,7 +43,13 @@ NOMINAL_INT8_TOPS = 4500.0
 # head, from ncu captures summarised under profiles/: c4 from a capture of a 4-head slice of c4
 # itself, c2 from a capture of the whole workload.  Every head has its own Q/K/V codes, vectors
 # and output, so the traffic of a launch is proportional to the heads it processes.
-FUSED_DRAM_BYTES_PER_HEAD = {"c4": None, "c2": 99.3e6 / 48}
+FUSED_DRAM_BYTES_PER_HEAD = {
+    # 4-head slice of c4: 52.55 MB read per launch (codes and vectors, each read once; K/V of a head stay in L2
+    # for all of its query tiles).  The slice's 33.5 MB of output were still in L2 when the kernel ended
+    # (3-6 MB written); the full workload's 335 MB cannot be, so the output bytes are counted as written.
+    "c4": 52.55e6 / 4 + 32760 * 128 * 2,
+    "c2": 99.3e6 / 48,
+}
 
 _JSON_OUT = None  # duplicate of the original standard output, set in main()
 

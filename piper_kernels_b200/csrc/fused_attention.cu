@@ -95,9 +95,9 @@ struct Cfg {
   static constexpr int LAUNCH_REGS = (65536 / THREADS) / 8 * 8;  // 128 registers per thread at launch
   // Per-role register budgets (setmaxnreg): the dequant rows hold head_dim FP32 numerators each.
   static constexpr bool SAGE64 = ALGO == kSage && D == 64;
-  static constexpr int REG_SM = SAGE64 ? 152 : 112;
-  static constexpr int REG_DQ = SAGE64 ? 144 : 240;
-  static constexpr int REG_HELPER = SAGE64 ? 56 : 48;
+  static constexpr int REG_SM = SAGE64 ? 152 : 120;
+  static constexpr int REG_DQ = SAGE64 ? 144 : 232;
+  static constexpr int REG_HELPER = SAGE64 ? 56 : 40;
   // Measured per operator: converged helper warps cut the issue cost of every copy and product
   // (the compiler keeps descriptors in uniform registers) and win for sage at head_dim 64, but all
   // 32 lanes then probe the mbarriers, which costs the piper kernel 5 % at long key sequences.

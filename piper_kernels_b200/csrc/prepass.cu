@@ -202,52 +202,70 @@ __global__ void __launch_bounds__(kThreads) row_range_kernel(TensorArg v, const 
 
 // ---------------------------------------------------------------------------------------
 // Stable ascending sort of one head's keys: least-significant-digit radix sort, 8 bits per
-// pass, one CTA per head; passes over a digit that all keys share are skipped (the sign and high
-// exponent bits of a row range usually are).  The row indices end in idx0 ("order").
+// pass, one CTA per head.  Every warp owns a contiguous segment of the current order.  A pass
+// is three steps with one CTA-wide barrier between them and none inside: (1) every warp counts
+// the digits of its segment into its own histogram; (2) 256 threads turn the 32 x 256 counts
+// into starting positions (digit-major, warp-minor, which keeps the order stable); (3) every
+// warp walks its segment again, 32 keys at a time, ranks equal digits inside the group with
+// match_any and moves keys and row indices to their positions.  A digit on which all keys agree
+// (the sign and high exponent bits of a row range usually are) costs only step (1).  The row
+// indices end in idx0 ("order").
 // ---------------------------------------------------------------------------------------
 constexpr int kSortThreads = 1024;
+constexpr int kSortWarps = kSortThreads / 32;
+constexpr int kSortBatch = 16;  // 32-key groups whose loads a warp issues before it ranks them
 
 __global__ void __launch_bounds__(kSortThreads) segment_sort_kernel(uint32_t* __restrict__ keys0,
                                                                     uint32_t* __restrict__ keys1,
                                                                     int32_t* __restrict__ idx0,
                                                                     int32_t* __restrict__ idx1, int n) {
-  __shared__ uint32_t hist[4][256];  // digit histograms of all four passes, from one read of the keys
-  __shared__ uint32_t base[256];
-  __shared__ uint32_t warp_cnt[kSortThreads / 32][256];
-  __shared__ int uniform[4];         // a digit on which every key agrees needs no pass
+  __shared__ uint32_t cnt[kSortWarps][256];  // per-warp digit counts, then per-warp write positions
+  __shared__ uint32_t total[256];
+  __shared__ int skip[4];  // passes whose digit every key shares
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const long long seg = static_cast<long long>(blockIdx.x) * n;
   uint32_t* kbuf[2] = {keys0 + seg, keys1 + seg};
   int32_t* ibuf[2] = {idx0 + seg, idx1 + seg};
+  // contiguous segment of this warp: a multiple of 32 keys so that groups never straddle warps
+  const int per_warp = ((n + kSortWarps - 1) / kSortWarps + 31) / 32 * 32;
+  const int w0 = min(n, warp * per_warp), w1 = min(n, w0 + per_warp);
 
-  for (int i = tid; i < 4 * 256; i += kSortThreads) (&hist[0][0])[i] = 0;
-  if (tid < 4) uniform[tid] = 0;
-  __syncthreads();
-  for (int i = tid; i < n; i += kSortThreads) {
-    const uint32_t key = kbuf[0][i];
-#pragma unroll
-    for (int d = 0; d < 4; ++d) atomicAdd(&hist[d][(key >> (8 * d)) & 0xFF], 1u);
-  }
-  __syncthreads();
-  for (int i = tid; i < 4 * 256; i += kSortThreads)
-    if ((&hist[0][0])[i] == static_cast<uint32_t>(n)) uniform[i >> 8] = 1;
-  __syncthreads();
-
+  if (tid < 4) skip[tid] = 0;  // visible to all after the first barrier below
   int cur = 0;        // which buffer pair holds the current order
-  bool first = true;  // the first pass that runs reads the implicit identity permutation
+  bool first = true;  // the first pass that moves data reads the implicit identity permutation
   for (int pass = 0; pass < 4; ++pass) {
-    if (uniform[pass]) continue;  // block-uniform decision
     const uint32_t* ksrc = kbuf[cur];
-    uint32_t* kdst = kbuf[cur ^ 1];
-    const int32_t* isrc = ibuf[cur];
-    int32_t* idst = ibuf[cur ^ 1];
     const int shift = pass * 8;
-
-    if (warp == 0) {  // exclusive scan of 256 counters, 8 per lane
+    // (1) per-warp histograms
+    for (int i = lane; i < 256; i += 32) cnt[warp][i] = 0;
+    __syncwarp();
+    for (int b0 = w0; b0 < w1; b0 += 32 * kSortBatch) {  // kSortBatch loads in flight per lane
+      uint32_t kk[kSortBatch];
+#pragma unroll
+      for (int u = 0; u < kSortBatch; ++u) {
+        const int i = b0 + u * 32 + lane;
+        kk[u] = i < w1 ? ksrc[i] : 0u;
+      }
+#pragma unroll
+      for (int u = 0; u < kSortBatch; ++u) {
+        if (b0 + u * 32 + lane < w1) atomicAdd(&cnt[warp][(kk[u] >> shift) & 0xFF], 1u);
+      }
+    }
+    __syncthreads();
+    // (2) positions: thread d owns digit d
+    if (tid < 256) {
+      uint32_t sum = 0;
+#pragma unroll 8
+      for (int w = 0; w < kSortWarps; ++w) sum += cnt[w][tid];
+      total[tid] = sum;
+      if (sum == static_cast<uint32_t>(n)) skip[pass] = 1;
+    }
+    __syncthreads();
+    if (warp == 0) {  // exclusive scan of the 256 digit totals, 8 per lane
       uint32_t c[8], sum = 0;
 #pragma unroll
       for (int i = 0; i < 8; ++i) {
-        c[i] = hist[pass][lane * 8 + i];
+        c[i] = total[lane * 8 + i];
         sum += c[i];
       }
       uint32_t incl = sum;
@@ -259,48 +277,61 @@ __global__ void __launch_bounds__(kSortThreads) segment_sort_kernel(uint32_t* __
       uint32_t run = incl - sum;
 #pragma unroll
       for (int i = 0; i < 8; ++i) {
-        base[lane * 8 + i] = run;
+        total[lane * 8 + i] = run;
         run += c[i];
       }
     }
     __syncthreads();
-
-    for (int c0 = 0; c0 < n; c0 += kSortThreads) {
-      const int i = c0 + tid;
-      const bool valid = i < n;
-      uint32_t key = 0;
-      int32_t idx = 0;
-      uint32_t digit = 256;
-      if (valid) {
-        key = ksrc[i];
-        idx = first ? i : isrc[i];
-        digit = (key >> shift) & 0xFF;
+    if (skip[pass]) continue;  // the same for every thread: written before the last barrier
+    if (tid < 256) {
+      uint32_t run = total[tid];
+#pragma unroll 8
+      for (int w = 0; w < kSortWarps; ++w) {
+        const uint32_t c = cnt[w][tid];
+        cnt[w][tid] = run;
+        run += c;
+      }
+    }
+    __syncthreads();
+    // (3) stable scatter, warp by warp in segment order
+    uint32_t* kdst = kbuf[cur ^ 1];
+    const int32_t* isrc = ibuf[cur];
+    int32_t* idst = ibuf[cur ^ 1];
+    for (int b0 = w0; b0 < w1; b0 += 32 * kSortBatch) {
+      uint32_t kk[kSortBatch];
+      int32_t ii[kSortBatch];
+#pragma unroll
+      for (int u = 0; u < kSortBatch; ++u) {  // all loads of the batch first
+        const int i = b0 + u * 32 + lane;
+        kk[u] = 0;
+        ii[u] = i;
+        if (i < w1) {
+          kk[u] = ksrc[i];
+          if (!first) ii[u] = isrc[i];
+        }
       }
 #pragma unroll
-      for (int j = 0; j < 8; ++j) warp_cnt[warp][lane * 8 + j] = 0;
-      __syncwarp();
-      const uint32_t peers = __match_any_sync(0xffffffffu, digit);
-      const uint32_t rank = __popc(peers & ((1u << lane) - 1u));
-      if (valid && rank == 0) warp_cnt[warp][digit] = __popc(peers);
-      __syncthreads();
-      if (tid < 256) {
-        uint32_t run = base[tid];
-#pragma unroll 8
-        for (int w = 0; w < kSortThreads / 32; ++w) {
-          const uint32_t c = warp_cnt[w][tid];
-          warp_cnt[w][tid] = run;
-          run += c;
+      for (int u = 0; u < kSortBatch; ++u) {
+        if (b0 + u * 32 >= w1) break;  // warp-uniform
+        const bool valid = b0 + u * 32 + lane < w1;
+        const uint32_t digit = valid ? ((kk[u] >> shift) & 0xFF) : 256u + lane;  // lanes past the end match nobody
+        const uint32_t peers = __match_any_sync(0xffffffffu, digit);
+        const uint32_t rank = __popc(peers & ((1u << lane) - 1u));
+        const int leader = __ffs(peers) - 1;
+        uint32_t base = 0;
+        if (valid && rank == 0) {
+          base = cnt[warp][digit];
+          cnt[warp][digit] = base + __popc(peers);
         }
-        base[tid] = run;
+        base = __shfl_sync(0xffffffffu, base, leader);
+        if (valid) {
+          kdst[base + rank] = kk[u];
+          idst[base + rank] = ii[u];
+        }
+        __syncwarp();
       }
-      __syncthreads();
-      if (valid) {
-        const uint32_t pos = warp_cnt[warp][digit] + rank;
-        kdst[pos] = key;
-        idst[pos] = idx;
-      }
-      __syncthreads();
     }
+    __syncthreads();  // the next pass reads what every warp has just written (same CTA: visible after the barrier)
     cur ^= 1;
     first = false;
   }
@@ -352,24 +383,35 @@ __global__ void __launch_bounds__(kThreads) quantize_qk_kernel(
 #pragma unroll
   for (int i = 0; i < 8; ++i) mu[i] = IS_KEY ? mean[bh * D + cg * 8 + i] : 0.f;
 
+  // All row indices first, then all row loads, then the arithmetic: NP 16-byte loads per thread
+  // are in flight at once (two dependent levels when rows are gathered through `order`).
   float vals[NP][8];
+  long long src[NP];
+#pragma unroll
+  for (int p = 0; p < NP; ++p) {
+    const int r = blk * kBlockRows + p * RPP + rl;
+    src[p] = -1;
+    if (r < len) src[p] = (IS_KEY && order != nullptr) ? order[static_cast<long long>(bh) * len + r] : r;
+  }
+#pragma unroll
+  for (int p = 0; p < NP; ++p) {
+    if (src[p] >= 0) {
+      load8<T, ALIGNED>(xp + src[p] * x.ss + cg * 8, vals[p]);
+    } else {
+#pragma unroll
+      for (int i = 0; i < 8; ++i) vals[p][i] = 0.f;
+    }
+  }
 #pragma unroll
   for (int p = 0; p < NP; ++p) {
     const int lr = p * RPP + rl;
-    const int r = blk * kBlockRows + lr;
     float m = 0.f;
-    if (r < len) {
-      long long src = r;
-      if (IS_KEY && order != nullptr) src = order[static_cast<long long>(bh) * len + r];
-      load8<T, ALIGNED>(xp + src * x.ss + cg * 8, vals[p]);
+    if (src[p] >= 0) {
 #pragma unroll
       for (int i = 0; i < 8; ++i) {
         if (IS_KEY) vals[p][i] = __fsub_rn(vals[p][i], mu[i]);
         m = fmaxf(m, fabsf(vals[p][i]));
       }
-    } else {
-#pragma unroll
-      for (int i = 0; i < 8; ++i) vals[p][i] = 0.f;
     }
 #pragma unroll
     for (int o = TPR / 2; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
@@ -460,26 +502,36 @@ __global__ void __launch_bounds__(kThreads) quantize_v_kernel(
   uint32_t packed[8];
 #pragma unroll
   for (int i = 0; i < 8; ++i) packed[i] = 0;
+  // row indices, then all row loads (NP 16-byte loads per thread in flight), then the arithmetic
+  long long src[NP];
+  float xs[NP][8];
+#pragma unroll
+  for (int p = 0; p < NP; ++p) {
+    const int r = blk * kBlockRows + rl * NP + p;
+    src[p] = -1;
+    if (r < sk) src[p] = (!SAGE && order != nullptr) ? order[static_cast<long long>(bh) * sk + r] : r;
+  }
+#pragma unroll
+  for (int p = 0; p < NP; ++p) {
+    if (src[p] >= 0) {
+      load8<T, ALIGNED>(vp + src[p] * v.ss + cg * 8, xs[p]);
+    } else {
+#pragma unroll
+      for (int i = 0; i < 8; ++i) xs[p][i] = 0.f;
+    }
+  }
 #pragma unroll
   for (int p = 0; p < NP; ++p) {
     const int lr = rl * NP + p;
     const int r = blk * kBlockRows + lr;
-    float x[8];
+    float (&x)[8] = xs[p];
     float m = 0.f;
-    if (r < sk) {
-      long long src = r;
-      if (!SAGE && order != nullptr) src = order[static_cast<long long>(bh) * sk + r];
-      load8<T, ALIGNED>(vp + src * v.ss + cg * 8, x);
-      if (!SAGE) {
+    if (r < sk && !SAGE) {
 #pragma unroll
-        for (int i = 0; i < 8; ++i) {
-          x[i] = __fsub_rn(x[i], aux[i]);
-          m = fmaxf(m, fabsf(x[i]));
-        }
+      for (int i = 0; i < 8; ++i) {
+        x[i] = __fsub_rn(x[i], aux[i]);
+        m = fmaxf(m, fabsf(x[i]));
       }
-    } else {
-#pragma unroll
-      for (int i = 0; i < 8; ++i) x[i] = 0.f;
     }
     if (!SAGE) {
 #pragma unroll

@@ -233,6 +233,38 @@ def test_key_order_with_ties_and_skipped_digit_passes():
         assert np.array_equal(order, np.argsort(rng, kind="stable").astype(np.int32))
 
 
+def _reference_functions():
+    """The reference project's own portable loops, when its package is installed beside the
+    oracle (oracle/_ref, filled by oracle/build_ref.py where the reference tree exists)."""
+    try:
+        from oracle.build_ref import import_reference
+        import_reference()
+        from piper_kernels.attention.piper.reference import reference_piper_attention
+        from piper_kernels.attention.sage2pp.reference import reference_sage_attention_2pp
+    except ImportError as exc:
+        pytest.skip(f"reference package not installed beside the oracle: {exc}")
+    return reference_piper_attention, reference_sage_attention_2pp
+
+
+@pytest.mark.parametrize("name,head", [("c2", 21), ("c5", 5), ("c1", 6)])
+def test_whole_head_against_the_reference_loop_on_cuda_tensors(name, head):
+    """Second, whole-tensor oracle: the reference's own portable loop (device-agnostic PyTorch)
+    run on CUDA tensors with FP32 inputs, against the FP32 output of the CUDA kernels."""
+    ref_piper, ref_sage = _reference_functions()
+    w = WORKLOADS[name]
+    q, k, v = make_inputs(w, "cuda", range(head, head + 1))
+    center, sort = _policy(w, q, k)
+    with torch.no_grad():
+        if w.op == "piper":
+            want = ref_piper(q.float(), k.float(), v.float(), w.head_dim ** -0.5, w.causal, center_value=center,
+                             qk_quantization="per_warp", sort_value_rows=sort)
+        else:
+            want = ref_sage(q.float(), k.float(), v.float(), w.head_dim ** -0.5, w.causal, qk_quantization="per_thread")
+    assert want.dtype == torch.float32
+    err = _gate32(_gpu32(w, q, k, v), want.cpu().numpy())
+    print(f"{name} head {head} vs the reference's loop on CUDA: max-abs {err:.3e}")
+
+
 def test_c4_size_constant_value_is_restored_exactly():
     w = WORKLOADS["c4"]
     q, k, _ = make_inputs(w, "cuda", range(0, 2))
