@@ -571,7 +571,10 @@ fused_attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
     // requested before the last chunk of tile j is folded.  Each chunk is re-armed once read.
     constexpr int NCH = DH / CH;
     static_assert(NCH >= 2, "the next tile's product is waited for before the last chunk");
-    constexpr int STAT_AT = 1;  // chunk after which the next tile's factors are evaluated and its product awaited
+    constexpr int STAT_AT = 1;  // chunk after which the next tile's factors are evaluated
+    // ... and the next tile's product awaited.  Any later chunk measured 4-6 % slower: the folds that
+    // then run while that product executes slow down by as much as the wait shortens.
+    constexpr int NEXT_AT = 1;
     uint32_t obuf[2][CH];
     const float2 neg_magic2 = make_float2(-kMagic, -kMagic);
     uint32_t armv[16];
@@ -609,6 +612,8 @@ fused_attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
           PK_STAMP(NSWG, j, 4);
           ok = advance_stats(j + 1);
           PK_STAMP(NSWG, j, 7);
+        }
+        if (ch == NEXT_AT && j + 1 < n_tiles) {
           ok = ok && WARP_ALL(mbar_wait_bounded(bars.pv_done((j + 1) % NPV), ((j + 1) / NPV) & 1, abort_flag, W_DQ_O, kLimit));
           tc_fence_after();
           PK_STAMP(NSWG, j, 5);
