@@ -2,10 +2,11 @@
 
     python -m oracle.time_reference_gpu [--workload c5] [--heads 4]
 
-Runs, on CUDA tensors, (a) the reference's portable PyTorch loop (device-agnostic) and (b) its
+Runs, on CUDA tensors, (a) the reference's portable PyTorch loop (device-agnostic), (b) its
 Triton backend through the reference's own dispatch (``sage_attention_2pp`` takes the Triton
 kernel on compute capability >= 8.9; ``piper_attention`` has no optimized backend on capability
-10.0 and falls back to the portable loop).  Whatever Triton emits for sm_100 is JIT output of
+10.0 and falls back to the portable loop) and (c) for Piper the Triton kernel with the affine
+signed-INT8 fallback through the reference's private entry point.  Whatever Triton emits for sm_100 is JIT output of
 the reference's kernels, not a shipped Blackwell kernel; a compile failure is reported as such.
 Prints one JSON line per measurement.  Nothing here is part of the product or of its benchmark.
 """
@@ -65,6 +66,12 @@ def main() -> None:
                                                 qk_quantization="per_warp", sort_value_rows=sort), 3)
         timed("reference public piper_attention on this GPU (its own dispatch)",
               lambda: ref.piper_attention(q, k, v, is_causal=w.causal), 3)
+        # The reference's Triton Piper kernel with the affine signed-INT8 PV fallback: plain tl.dot, no
+        # compiler hook, reachable on any capability through its private entry (piper/triton.py:1292-1316).
+        from piper_kernels.attention.piper.triton import _run_piper_attention
+        timed("reference Triton JIT Piper kernel, affine INT8 PV fallback (_run_piper_attention, native_uint8=False)",
+              lambda: _run_piper_attention(q, k, v, scale, w.causal, center, native_uint8=False, sort_value_rows=False,
+                                           use_tensor_descriptors=False), 10)
     else:
         timed("reference portable loop on CUDA tensors (reference_sage_attention_2pp)",
               lambda: reference_sage_attention_2pp(q.float(), k.float(), v.float(), scale, w.causal, qk_quantization="per_thread"), 3)
