@@ -472,7 +472,7 @@ def ours_arm(args, w, rank, local_rank, world):
         kwargs = dict(is_causal=w.causal, center_value=w.center) if w.op == "piper" else dict(is_causal=w.causal)
         fn = pk.piper_attention if w.op == "piper" else pk.sage_attention_2pp
         local_heads = q.shape[0] * q.shape[1]
-        chunk = max(1, min(4, local_heads // 4))
+        chunk = max(1, min(8, local_heads // 4))
         pipe = HostAttentionPipeline(dev, heads_per_chunk=chunk)
 
         def e2e_step():
@@ -560,11 +560,14 @@ def ours_arm(args, w, rank, local_rank, world):
         cpu_baseline = {"value": tops, "unit": UNIT, "cores": threads, "kind": kind, "sample": desc}
 
     prepass_launches = 6 + (2 if sort else 0)
+    # heads with few query tiles split their keys over several CTAs and add a merge launch (piper only)
+    n_qt, n_kt = -(-w.q_len // 128), -(-w.kv_len // 64)
+    key_split = w.op == "piper" and not w.causal and n_qt <= 8 and min(8, 16 // n_qt, n_kt // 4) >= 2
     line = {
         "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": warmup,
         "ms_per_step": ms, "higher_is_better": True, "scaling": args.scaling, "vs_baseline": None, "dtype": "int8",
         "data": "synthetic", "config": workload_config(w, world, args.scaling, heads_per_rank), "clocks": clocks, "e2e": e2e,
-        "gpu_launches": (prepass_launches + 1) * args.steps, "roofline": roofline, "cpu_baseline": cpu_baseline,
+        "gpu_launches": (prepass_launches + 1 + (1 if key_split else 0)) * args.steps, "roofline": roofline, "cpu_baseline": cpu_baseline,
         "roofline_prepass": roofline_prepass, "device_status": status[0],
         "per_gpu_value": value / world,
         "value_full_rectangle": (4.0 * total_heads * w.q_len * w.kv_len * w.head_dim / (ms * 1e-3) / 1e12) if w.causal else None,

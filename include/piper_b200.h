@@ -1,7 +1,9 @@
 /* piper_b200.h — C ABI of libpiper_b200.so: fused quantized attention forward for NVIDIA B200
  * (sm_100a).  Plain pointers and sizes only; no torch types.  All entry points are
  * re-entrant, launch on the caller's stream of the caller's device, never allocate device
- * memory and never synchronise (except pk_device_status, which the caller asks for).
+ * memory and never synchronise (except pk_device_status, which the caller asks for).  The one
+ * allocation the library ever makes is four bytes of pinned host memory per device, at the
+ * first fused-kernel launch on that device (the fault word read by pk_poll_device_fault).
  *
  * The library replaces, for this one path, the operators that the reference project
  * (Boffee/piper-kernels) registers as
@@ -104,6 +106,12 @@ PK_API const char* pk_last_error(void);
  * (piper/triton.py:1054-1289) behind piper_kernels::piper_attention (:1319-1336). */
 PK_API int pk_piper_workspace_bytes(const pk_problem* p, uint64_t* bytes);
 PK_API int pk_piper_prepare(const pk_problem* p, pk_views* views); /* prepass only (piper/triton.py:1054-1236) */
+/* Heads with at most 1024 query rows (non-causal): pk_piper_run splits every query tile's keys over up
+ * to eight CTAs and merges their un-normalised rows in a second launch, so that short-query problems
+ * fill the GPU (the role of the reference's select_query_block, attention/scheduling.py:7-19, which
+ * shrinks the query tile instead).  The split depends on q_len and kv_len only, never on batch*heads:
+ * a head's output is bit-identical whichever heads share its call.  The workspace size includes the
+ * partial rows. */
 PK_API int pk_piper_run(const pk_problem* p);                      /* fused kernel on a prepared workspace (:1239-1289) */
 /* Prepared key/value reuse: the reference's benchmarks split every provider into prepare() and
  * run(prepared) (benchmarks/lib/attention_providers.py:201-216); cross-attention and diffusion

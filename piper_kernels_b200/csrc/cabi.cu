@@ -63,6 +63,29 @@ Layout make_layout(const pk_problem& p, Algo algo) {
   L.k_mul = take(BH * L.sk_pad * 4);
   L.k_add = take(BH * L.sk_pad * 4);
   L.k_inv = take(BH * L.sk_pad * 4);
+  // Key-split policy: the counterpart of the reference's select_query_block (attention/scheduling.py:7-19),
+  // which shrinks the query tile until every SM has a CTA.  Here the query tile stays 128 rows and, for
+  // heads with few query tiles, the keys are split so that a head contributes about 16 CTAs.  The count
+  // depends on the head's own shape only, never on batch*heads: a head's result is bit-identical
+  // whichever other heads share its call (and however heads are sharded over GPUs).  Piper only: its
+  // probability codes depend on a tile's own maximum, so a split changes nothing but the order of the
+  // FP32 sums; Sage quantises probabilities against the running maximum, which a split would restart.
+  L.splits = 1;
+  L.tiles_per_split = L.sk_pad / kKeyTile;
+  {
+    const int n_qt = L.sq_pad / kQTile, n_all = L.sk_pad / kKeyTile;
+    if (algo == kPiper && !p.is_causal && n_qt <= kSplitBelowQueryTiles) {
+      int want = kCtasPerSmallHead / n_qt;
+      if (want > kMaxKeySplits) want = kMaxKeySplits;
+      if (want > n_all / kMinTilesPerSplit) want = n_all / kMinTilesPerSplit;
+      if (want >= 2) {
+        L.tiles_per_split = (n_all + want - 1) / want;
+        L.splits = (n_all + L.tiles_per_split - 1) / L.tiles_per_split;  // no empty split
+      }
+    }
+  }
+  L.partial = 0;
+  if (L.splits > 1) L.partial = take(BH * L.sq_pad * static_cast<size_t>(L.splits) * partial_row_floats(L.D) * 4);
   if (algo == kPiper && p.sort_value_rows) {
     L.range = take(BH * L.Sk * 4);
     L.keys_alt = take(BH * L.Sk * 4);

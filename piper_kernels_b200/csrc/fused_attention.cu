@@ -34,6 +34,9 @@
 // multicast; every wait is time-limited.
 
 #include <cuda.h>
+
+#include <atomic>
+
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 #include <cuda_fp8.h>
@@ -83,6 +86,8 @@ struct FusedParams {
   int dump_bh, dump_qt;
   long long* timeline;  // optional [6][timeline_tiles][4] clock stamps of CTA (dump_bh, dump_qt)
   int timeline_tiles;
+  int splits, tiles_per_split;  // key split of small problems (1: none); CTA z handles tiles [z*tps, (z+1)*tps)
+  float* partial;               // [BH, sq_pad, splits, D + 4] numerators, running max, denominator (splits > 1)
   int skip_key_tile;        // stalled-wait drill only: key tile whose copy the producer leaves out
   int32_t* host_status;     // optional pinned host word (device-visible) that also receives the code
 };
@@ -226,7 +231,9 @@ fused_attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
   const int qt = causal ? (n_qt - 1 - blockIdx.x) : blockIdx.x;  // causal: longest tiles first
   const int q0 = qt * kQTile;
   const int n_all = prm.sk_pad / kKeyTile;
-  const int n_tiles = causal ? min(n_all, 2 * qt + 2) : n_all;
+  // key tiles of this CTA: all of them, those at or below the diagonal (causal), or one split's share
+  const int t_begin = blockIdx.z * prm.tiles_per_split;
+  const int n_tiles = causal ? min(n_all, 2 * qt + 2) : min(n_all - t_begin, prm.tiles_per_split);
   // DUMP instantiations (debug entry point only) copy the first key tile's intermediates out
   const bool dumping = DUMP && prm.dump != nullptr && bh == prm.dump_bh && qt == prm.dump_qt;
   const bool stamping = TIMELINE && prm.timeline != nullptr && bh == prm.dump_bh && qt == prm.dump_qt &&
@@ -286,17 +293,17 @@ fused_attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
       if (HELECT) {
         if (!(DRILL && i == prm.skip_key_tile)) {
           mbar_expect_tx(bars.k_full(ks), C::K_BYTES);
-          tma_load_2d(smem_base + C::OFF_K + ks * C::K_BYTES, &tm_k, bars.k_full(ks), 0, bh * prm.sk_pad + i * kKeyTile);
+          tma_load_2d(smem_base + C::OFF_K + ks * C::K_BYTES, &tm_k, bars.k_full(ks), 0, bh * prm.sk_pad + (t_begin + i) * kKeyTile);
         }
         const uint32_t vdst = smem_base + C::OFF_VEC + cs * VEC_FLOATS * 4;
         const uint32_t vbar = bars.vec_full(cs);
         mbar_expect_tx(vbar, VEC_FLOATS * 4);
-        const long long off = vec_base + static_cast<long long>(i) * kKeyTile;
+        const long long off = vec_base + static_cast<long long>(t_begin + i) * kKeyTile;
         bulk_load(vdst, prm.k_mul + off, kKeyTile * 4, vbar);
         bulk_load(vdst + kKeyTile * 4, prm.k_add + off, kKeyTile * 4, vbar);
         bulk_load(vdst + 2 * kKeyTile * 4, prm.k_inv + off, kKeyTile * 4, vbar);
         mbar_expect_tx(bars.v_full(vs), C::V_BYTES);
-        tma_load_2d(smem_base + C::OFF_V + vs * C::V_BYTES, &tm_v, bars.v_full(vs), i * kKeyTile, bh * D);
+        tma_load_2d(smem_base + C::OFF_V + vs * C::V_BYTES, &tm_v, bars.v_full(vs), (t_begin + i) * kKeyTile, bh * D);
       }
       last = i;
       PK_STAMP(NSWG + 3, i, 2);
@@ -647,7 +654,7 @@ fused_attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
     }
     // epilogue: normalise, restore the V mean (piper) / apply the channel scale (sage), cast
     const int grow = q0 + row;
-    if (!ok && grow < prm.Sq) {
+    if (!ok && grow < prm.Sq && prm.splits == 1) {
       // A wait was abandoned: this tile's rows are not valid.  They are filled with NaN so that a
       // caller who never reads the status words cannot mistake them for results.
       const long long obase = (static_cast<long long>(bh) * prm.Sq + grow) * D + col0;
@@ -656,7 +663,18 @@ fused_attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
         else static_cast<uint16_t*>(prm.out)[obase + d0] = (prm.out_dtype == PK_F16) ? 0x7E00 : 0x7FC0;
       }
     }
-    if (ok && grow < prm.Sq) {
+    if (prm.splits > 1) {
+      // Key-split launch: leave the un-normalised row (numerators relative to 2^max, the running
+      // maximum and the denominator) for the merge kernel.  Padding rows are written too (zeros).
+      float mx = m;  // piper: tracked here; sage: the softmax warpgroups' last hand-over value
+      if (ALGO == kSage) mx = n_tiles > 0 ? m_ring[((n_tiles - 1) % NM) * kQTile + row] : -INFINITY;
+      float* pr = prm.partial + ((static_cast<long long>(bh) * prm.sq_pad + q0 + row) * prm.splits + blockIdx.z) * (D + 4) + col0;
+      const float bad = __int_as_float(0x7FC00000);
+#pragma unroll
+      for (int d0 = 0; d0 < DH; d0 += 4)
+        *reinterpret_cast<float4*>(pr + d0) = make_float4(num2[d0 / 2].x, num2[d0 / 2].y, num2[d0 / 2 + 1].x, num2[d0 / 2 + 1].y);
+      *reinterpret_cast<float4*>(pr + DH) = make_float4(mx, ok ? den : bad, 0.f, 0.f);
+    } else if (ok && grow < prm.Sq) {
       // one IEEE division per row; the D per-element divisions of the reference become
       // multiplications by the reciprocal (at most an ulp apart, and far less code)
       const float dinv = __fdiv_rn(1.f, fmaxf(den, 1e-30f));
@@ -702,6 +720,48 @@ fused_attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
   if (tid == 0 && *abort_flag != 0) {
     atomicCAS(prm.status, 0, *abort_flag);
     if (prm.host_status != nullptr) atomicCAS_system(prm.host_status, 0, *abort_flag);
+  }
+}
+
+// ---------------------------------------------------------------------------------------
+// Merge of a key-split launch: one warp per query row combines the splits' un-normalised rows,
+// out = sum_s num_s 2^(m_s - M) / sum_s den_s 2^(m_s - M), then the usual epilogue.
+// ---------------------------------------------------------------------------------------
+template <int D, int ALGO>
+__global__ void __launch_bounds__(256) merge_splits_kernel(const float* __restrict__ partial, const float* __restrict__ v_aux,
+                                                           void* __restrict__ out, int out_dtype, int Sq, int sq_pad,
+                                                           int splits, long long rows_total) {
+  constexpr int VEC = D / 32;  // columns per lane
+  const long long gw = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
+  const int lane = threadIdx.x & 31;
+  if (gw >= rows_total) return;
+  const long long bh = gw / Sq;
+  const int row = static_cast<int>(gw % Sq);
+  const float* pr = partial + ((bh * sq_pad + row) * splits) * (D + 4);
+  float mx = -INFINITY;
+  for (int s = 0; s < splits; ++s) mx = fmaxf(mx, pr[s * (D + 4) + D]);
+  float den = 0.f, acc[VEC];
+  bool bad = false;
+#pragma unroll
+  for (int i = 0; i < VEC; ++i) acc[i] = 0.f;
+  for (int s = 0; s < splits; ++s) {
+    const float* ps = pr + s * (D + 4);
+    const float ms = ps[D], ds = ps[D + 1];
+    bad |= ds != ds;  // a split that gave up a wait marks its denominator
+    const float w = (ms == mx) ? 1.f : ex2_approx(ms - mx);
+    den = fmaf(ds, w, den);
+#pragma unroll
+    for (int i = 0; i < VEC; ++i) acc[i] = fmaf(ps[lane * VEC + i], w, acc[i]);
+  }
+  const float dinv = bad ? __int_as_float(0x7FC00000) : __fdiv_rn(1.f, fmaxf(den, 1e-30f));
+  const float* aux = v_aux + bh * D + lane * VEC;
+  const long long obase = (bh * Sq + row) * D + lane * VEC;
+#pragma unroll
+  for (int i = 0; i < VEC; ++i) {
+    const float r = (ALGO == kPiper) ? fmaf(acc[i], dinv, aux[i]) : acc[i] * (aux[i] * (1.f / 448.f)) * dinv;
+    if (out_dtype == PK_F32) static_cast<float*>(out)[obase + i] = r;
+    else if (out_dtype == PK_F16) static_cast<__half*>(out)[obase + i] = __float2half_rn(r);
+    else static_cast<__nv_bfloat16*>(out)[obase + i] = __float2bfloat16_rn(r);
   }
 }
 
@@ -766,15 +826,33 @@ int launch_one_impl(const pk_problem& p, const Layout& L, cudaStream_t st, const
   prm.timeline_tiles = dump ? dump->timeline_tiles : 0;
   prm.skip_key_tile = dump ? dump->skip_key_tile : -1;
   prm.host_status = fault_word_device_ptr(p.device);
+  // the debug instantiations always run unsplit
+  const int splits = (DEBUG == 0) ? L.splits : 1;
+  prm.splits = splits;
+  prm.tiles_per_split = splits > 1 ? L.tiles_per_split : L.sk_pad / kKeyTile;
+  prm.partial = splits > 1 ? at<float>(p, L.partial) : nullptr;
   auto kern = fused_attention_kernel<D, ALGO, KPB, CAUSAL, DEBUG>;
   {
-    const cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES);
-    if (e != cudaSuccess) return fail(PK_ERR_CUDA, "cudaFuncSetAttribute: %s", cuda_err(e));
+    // the attribute is per function and device: set it once
+    static std::atomic<bool> done[64];
+    const int dev = (p.device >= 0 && p.device < 64) ? p.device : 0;
+    if (!done[dev].load(std::memory_order_acquire)) {
+      const cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES);
+      if (e != cudaSuccess) return fail(PK_ERR_CUDA, "cudaFuncSetAttribute: %s", cuda_err(e));
+      done[dev].store(true, std::memory_order_release);
+    }
   }
-  const dim3 grid(L.sq_pad / kQTile, L.BH);
+  const dim3 grid(L.sq_pad / kQTile, L.BH, splits);
   kern<<<grid, C::THREADS, C::SMEM_BYTES, st>>>(tq, tk, tv, prm);
-  const cudaError_t e = cudaGetLastError();
+  cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return fail(PK_ERR_CUDA, "fused kernel launch failed: %s", cuda_err(e));
+  if (splits > 1) {
+    const long long rows = static_cast<long long>(L.BH) * L.Sq;
+    const unsigned blocks = static_cast<unsigned>((rows * 32 + 255) / 256);
+    merge_splits_kernel<D, ALGO><<<blocks, 256, 0, st>>>(prm.partial, prm.v_aux, p.out, p.out_dtype, L.Sq, L.sq_pad, splits, rows);
+    e = cudaGetLastError();
+    if (e != cudaSuccess) return fail(PK_ERR_CUDA, "merge kernel launch failed: %s", cuda_err(e));
+  }
   return PK_OK;
 }
 

@@ -20,9 +20,19 @@ enum Algo : int { kPiper = 0, kSage = 1 };
 struct Layout {
   int BH, D, Sq, Sk, sq_pad, sk_pad, chunks;
   int q_groups, k_groups;  // entries per head of the group-scale arrays
+  // Heads with few query tiles (non-causal): the key tiles of every query tile are split over
+  // `splits` CTAs of `tiles_per_split` tiles each, which leave un-normalised partial results in
+  // `partial`; a merge kernel combines them.  splits == 1: no split.
+  int splits, tiles_per_split;
   size_t status, k_mean, v_mean, k_part, v_part, q_codes, k_codes, v_codes, q_gscale, k_gscale,
-      v_scale, q_mul, k_mul, k_add, k_inv, range, keys_alt, idx_a, idx_b, total;
+      v_scale, q_mul, k_mul, k_add, k_inv, range, keys_alt, idx_a, idx_b, partial, total;
 };
+
+constexpr int kSplitBelowQueryTiles = 8;  // heads of up to 1024 query rows are candidates
+constexpr int kCtasPerSmallHead = 16;     // CTAs such a head should contribute
+constexpr int kMaxKeySplits = 8;
+constexpr int kMinTilesPerSplit = 4;  // a CTA's pipeline needs a few tiles to fill
+inline int partial_row_floats(int head_dim) { return head_dim + 4; }  // numerators, running max, denominator, padding
 
 Layout make_layout(const pk_problem& p, Algo algo);
 

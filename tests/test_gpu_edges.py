@@ -81,6 +81,29 @@ def test_causal_lengths(s):
     _check16(_np(pk.sage_attention_2pp(q, k, v, is_causal=True)), out, torch.bfloat16)
 
 
+@pytest.mark.parametrize("sq,sk,d", [(128, 4096, 128), (1, 2048, 64), (300, 1000, 64), (1000, 1077, 128), (64, 520, 128)])
+def test_key_split_of_short_query_heads(sq, sk, d):
+    """Piper heads with few query tiles split their keys over several CTAs (up to 8, at least four key
+    tiles each) and a merge kernel combines the un-normalised partial rows.  The split depends on the
+    head's shape only, so a head alone equals the same head inside a batch bit for bit.  Sage never
+    splits (its probability codes depend on the running maximum) and is checked on the same shapes."""
+    q = _rand((2, 3, sq, d), torch.bfloat16, 900 + sq)
+    k = _rand((2, 3, sk, d), torch.bfloat16, 901 + sk, shift=0.5)
+    v = _rand((2, 3, sk, d), torch.bfloat16, 902 + sk, shift=1.0)
+    out = _out32("piper", q, k, v, d ** -0.5, False, center=True)
+    want = oracle.piper_attention_oracle(_np(q), _np(k), _np(v), d ** -0.5, False, center_value=True,
+                                         qk_quantization="per_warp")
+    assert np.abs(out - want).max() <= MAX_ABS and cosine(out, want) >= MIN_COS
+    whole = pk.piper_attention(q, k, v, center_value=True)
+    _check16(_np(whole), out, torch.bfloat16)
+    one = pk.piper_attention(q[1:, 2:], k[1:, 2:], v[1:, 2:], center_value=True)
+    assert torch.equal(one, whole[1:, 2:])
+    out = _out32("sage2pp", q, k, v, d ** -0.5, False)
+    want = oracle.sage_attention_2pp_oracle(_np(q), _np(k), _np(v), d ** -0.5, False, qk_quantization="per_thread")
+    assert np.abs(out - want).max() <= MAX_ABS and cosine(out, want) >= MIN_COS
+    _check16(_np(pk.sage_attention_2pp(q, k, v)), out, torch.bfloat16)
+
+
 def test_many_small_heads_and_custom_scale():
     """128 heads of 72 keys with a sharp softmax (scale 0.2).  Here one probability code is worth
     up to 1/255 of a value: in a row that two or three keys dominate, a code that rounds the other
