@@ -1,6 +1,6 @@
 """Install the reference project's own attention package next to the oracle (TEST INFRASTRUCTURE).
 
-    python -m oracle.build_ref [--source /path/to/reference/src]
+    python -m oracle.build_ref [--source /path/to/reference/src]      (default: $PIPER_REF_SRC, then ../reference/src)
 
 The reference (Boffee/piper-kernels) is pure Python: its ``piper_kernels.attention`` package holds
 the portable quantized PyTorch loops (``attention/piper/reference.py``,
@@ -21,13 +21,16 @@ benchmark.  The product package never imports it.
 from __future__ import annotations
 
 import argparse
+import os
 import shutil
 import sys
 from pathlib import Path
 
 HERE = Path(__file__).resolve().parent
 DEST = HERE / "_ref"
-DEFAULT_SOURCES = (Path("/root/reference/src"),)
+# where the reference's src/ directory is looked for: $PIPER_REF_SRC, then a checkout named
+# "reference" beside this repository
+DEFAULT_SOURCES = tuple(Path(x) for x in (os.environ.get("PIPER_REF_SRC"), HERE.parents[1] / "reference" / "src") if x)
 PARTS = ("__init__.py", "attention", "_triton")
 
 
