@@ -48,12 +48,14 @@
 // abandoned.
 #define WARP_ALL(x) __all_sync(0xffffffffu, (x))
 #define WARP_ANY(x) __any_sync(0xffffffffu, (x))
-// The three helper warps (producer, two issue warps) either run their loops with lane 0 alone, or
-// with all 32 lanes and issue from the lane elect.sync picks (Cfg::HELPERS_CONVERGED).  HLANE
-// admits the lanes that run the loop, HWAIT wraps a wait, HELECT guards the issuing instructions.
-#define HLANE (C::HELPERS_CONVERGED || lane == 0)
-#define HWAIT(x) (C::HELPERS_CONVERGED ? WARP_ALL(x) : (x))
-#define HELECT (C::HELPERS_CONVERGED ? elect_one() : true)
+// A helper warp (producer, S issue, PV issue) runs its loop either with lane 0 alone or with all
+// 32 lanes, issuing from the lane elect.sync picks.  HCONV says which for the role being
+// compiled (HROLE_CONVERGED is set in front of each role), HLANE admits the lanes that run the
+// loop, HWAIT wraps a wait, HELECT guards the issuing instructions.
+#define HCONV (HROLE_CONVERGED)
+#define HLANE (HCONV || lane == 0)
+#define HWAIT(x) (HCONV ? WARP_ALL(x) : (x))
+#define HELECT (HCONV ? elect_one() : true)
 namespace pk {
 namespace {
 
@@ -103,10 +105,11 @@ struct Cfg {
   static constexpr int REG_SM = SAGE64 ? 152 : 120;
   static constexpr int REG_DQ = SAGE64 ? 144 : 232;
   static constexpr int REG_HELPER = SAGE64 ? 56 : 40;
-  // Measured per operator: converged helper warps cut the issue cost of every copy and product
-  // (the compiler keeps descriptors in uniform registers) and win for sage at head_dim 64, but all
-  // 32 lanes then probe the mbarriers, which costs the piper kernel 5 % at long key sequences.
-  static constexpr bool HELPERS_CONVERGED = ALGO == kSage;
+  // The two issue warps run converged and issue from the lane elect.sync picks: the compiler then
+  // keeps descriptors and addresses in uniform registers (47 instead of about 80 cycles per issued
+  // product).  The producer does the same for sage; for piper at long key sequences it measured
+  // 1-2 % faster with lane 0 running the loop alone.
+  static constexpr bool PRODUCER_CONVERGED = ALGO == kSage;
   // setmaxnreg only moves registers between the warps of the CTA: an increase waits (without a time
   // limit) until other warps have released enough, so the budgets must fit what the CTA was launched with.
   static_assert((NSWG * REG_SM + NDQ * REG_DQ + REG_HELPER) * 128 <= THREADS * LAUNCH_REGS,
@@ -271,6 +274,7 @@ fused_attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
   // resizes its allocation on entry.
   if (wg == NSWG + C::NDQ) setmaxnreg_dec<C::REG_HELPER>();
 
+#define HROLE_CONVERGED C::PRODUCER_CONVERGED
   if (warp == PROD_WARP && HLANE) {
     // ------------------------------------------------------------------ producer
     // All 32 lanes run the loop and the waits; the elected lane issues the copies.
@@ -319,6 +323,8 @@ fused_attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
       for (int t = max(0, last - NVEC + 1); t <= last; ++t) mbar_wait_quiet(bars.vec_full(t % NVEC), (t / NVEC) & 1, kDrain);
       for (int t = max(0, last - NV + 1); t <= last; ++t) mbar_wait_quiet(bars.v_full(t % NV), (t / NV) & 1, kDrain);
     }
+#undef HROLE_CONVERGED
+#define HROLE_CONVERGED true
   } else if (warp == QK_WARP && HLANE) {
     // ------------------------------------------------------------------ S = Q K^T issue
     // The two products are issued by two different warps.  S_j is issued as soon as K tile j has
@@ -367,6 +373,7 @@ fused_attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
       }
       PK_STAMP(NSWG + 2, j, 2);
     }
+#undef HROLE_CONVERGED
   } else if (wg == NSWG + C::NDQ) {
     // idle lanes / the fourth helper warp
   } else if (wg < NSWG) {
@@ -548,7 +555,8 @@ fused_attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
     // Row statistics recurrence (running max, denominator, rescale factors).  It depends only on
     // the per-tile statistics that the softmax warpgroups publish several tiles ahead, so the
     // factors of tile j+1 are evaluated early in the fold of tile j, where the chain of dependent
-    // instructions (shared-memory load, two exponentials) overlaps the fold arithmetic.
+    // instructions (shared-memory load, an exponential) overlaps the fold arithmetic.
+    constexpr float kRescaleThreshold = 8.f;
     float ow = 1.f, c = 0.f;      // factors of the tile being folded
     float ow_n = 1.f, c_n = 0.f;  // factors of the next tile
     auto advance_stats = [&](int j) -> bool {
@@ -556,16 +564,17 @@ fused_attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
       const float2 st = stat_ring[(j % NSTAT) * kQTile + row];
       if (ALGO == kPiper) {
         const float bm = st.x;
-        const float nm = fmaxf(m, bm);
+        // `m` is the exponent the numerators and the denominator are relative to.  It follows the
+        // tiles' maxima lazily: only a tile whose maximum exceeds it by more than
+        // kRescaleThreshold moves it (and costs a pass over the numerator row); otherwise the
+        // tile's weight 2^(bm - m) simply exceeds one, by at most 2^kRescaleThreshold.  num / den
+        // is the same quotient for any reference exponent; only FP32 rounding differs (1e-7).
         float cw;
-        if (nm == -INFINITY) { ow_n = 1.f; cw = 0.f; }
-        else {
-          ow_n = (m == nm) ? 1.f : ex2_approx(m - nm);
-          cw = (bm == nm) ? 1.f : ex2_approx(bm - nm);
-        }
+        if (bm == -INFINITY) { ow_n = 1.f; cw = 0.f; }
+        else if (bm > m + kRescaleThreshold) { ow_n = ex2_approx(m - bm); cw = 1.f; m = bm; }
+        else { ow_n = 1.f; cw = ex2_approx(bm - m); }
         den = fmaf(den, ow_n, st.y * cw);
         c_n = cw * (1.f / 255.f);
-        m = nm;
       } else {
         ow_n = st.x;
         den = fmaf(den, ow_n, st.y);
