@@ -559,7 +559,9 @@ def ours_arm(args, w, rank, local_rank, world):
         tops, kind, desc = cpu_reference_tops(w, args.cpu_seconds, threads)
         cpu_baseline = {"value": tops, "unit": UNIT, "cores": threads, "kind": kind, "sample": desc}
 
-    prepass_launches = 6 + (2 if sort else 0)
+    # status words, Q codes, column statistics (two launches), K codes, V codes; with a key order the row ranges are one
+    # more launch and the sort shares its launch with the Q codes
+    prepass_launches = 6 + (1 if sort else 0)
     # heads with few query tiles split their keys over several CTAs and add a merge launch (piper only)
     n_qt, n_kt = -(-w.q_len // 128), -(-w.kv_len // 64)
     key_split = w.op == "piper" and not w.causal and n_qt <= 8 and min(8, 16 // n_qt, n_kt // 4) >= 2

@@ -110,6 +110,7 @@ struct Cfg {
   // product).  The producer does the same for sage; for piper at long key sequences it measured
   // 1-2 % faster with lane 0 running the loop alone.
   static constexpr bool PRODUCER_CONVERGED = ALGO == kSage;
+  static constexpr int PRODUCER_SLEEP_NS = ALGO == kPiper ? 500 : 0;
   // setmaxnreg only moves registers between the warps of the CTA: an increase waits (without a time
   // limit) until other warps have released enough, so the budgets must fit what the CTA was launched with.
   static_assert((NSWG * REG_SM + NDQ * REG_DQ + REG_HELPER) * 128 <= THREADS * LAUNCH_REGS,
@@ -285,15 +286,22 @@ fused_attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
     }
     const long long vec_base = static_cast<long long>(bh) * prm.sk_pad;
     int last = -1;  // last key tile whose copies were issued
+    // The producer runs a whole ring ahead of the products, so its waits have microseconds of
+    // slack: the piper producer sleeps between probes instead of taking issue slots from the
+    // compute warps of its scheduler (1.5 % at long key sequences; nothing for sage).
+    auto producer_wait = [&](uint32_t bar, uint32_t parity, int where) -> bool {
+      if (C::PRODUCER_SLEEP_NS > 0) return mbar_wait_relaxed<(C::PRODUCER_SLEEP_NS > 0 ? C::PRODUCER_SLEEP_NS : 1)>(bar, parity, abort_flag, where, kLimit);
+      return mbar_wait_bounded(bar, parity, abort_flag, where, kLimit);
+    };
     for (int i = 0; i < n_tiles; ++i) {
       PK_STAMP(NSWG + 3, i, 0);
       const int ks = i % NK, vs = i % NV, cs = i % NVEC;
       // K stage ks was last read by S_{i-NK}, V stage vs by PV_{i-NV}.  The vector slot of tile
       // i-NVEC was last read before the probabilities of that tile were published, which
       // precedes the completion of S_{i-NK} (NVEC >= NK + NS + 2).
-      if (i >= NK && !HWAIT(mbar_wait_bounded(bars.qk_done(ks), ((i / NK) - 1) & 1, abort_flag, W_PROD_K, kLimit))) break;
+      if (i >= NK && !HWAIT(producer_wait(bars.qk_done(ks), ((i / NK) - 1) & 1, W_PROD_K))) break;
       PK_STAMP(NSWG + 3, i, 1);
-      if (i >= NV && !HWAIT(mbar_wait_bounded(bars.pv_done(i % NPV), ((i / NPV) - 1) & 1, abort_flag, W_PROD_V, kLimit))) break;
+      if (i >= NV && !HWAIT(producer_wait(bars.pv_done(i % NPV), ((i / NPV) - 1) & 1, W_PROD_V))) break;
       if (HELECT) {
         if (!(DRILL && i == prm.skip_key_tile)) {
           mbar_expect_tx(bars.k_full(ks), C::K_BYTES);

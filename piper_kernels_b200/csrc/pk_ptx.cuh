@@ -99,6 +99,28 @@ __device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity,
   return mbar_wait_slow(bar, parity, abort_flag, where, limit);
 }
 
+// The same wait for a role with slack (one whose result is not needed for several key tiles):
+// between probes the warp sleeps, so that its probe loop does not take issue slots from the
+// compute warps of its scheduler.
+template <int SLEEP_NS>
+__device__ __forceinline__ bool mbar_wait_relaxed(uint32_t bar, uint32_t parity, volatile int* abort_flag,
+                                                  int where, long long limit = kWaitCycleLimit) {
+  if (mbar_try_wait(bar, parity)) return true;
+  const long long t0 = clock64();
+  int n = 0;
+  while (true) {
+    __nanosleep(SLEEP_NS);
+    if (mbar_try_wait(bar, parity)) return true;
+    if ((++n & 63) == 0) {
+      if (*abort_flag != 0) return false;
+      if (clock64() - t0 > limit) {
+        *abort_flag = where;
+        return false;
+      }
+    }
+  }
+}
+
 // Waits at most `limit` cycles for a phase without raising the abort flag (used to let copies
 // that are still in flight land before a CTA that is giving up returns).
 __device__ __forceinline__ void mbar_wait_quiet(uint32_t bar, uint32_t parity, long long limit) {
