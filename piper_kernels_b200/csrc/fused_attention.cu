@@ -243,25 +243,25 @@ fused_attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
   const bool stamping = TIMELINE && prm.timeline != nullptr && bh == prm.dump_bh && qt == prm.dump_qt &&
                         ((tid & 127) == 0 || (lane == 0 && wg == NSWG + C::NDQ));
 
-  if (tid == 0) {
-    mbar_init(bars.q_full(), 1);
-    for (int i = 0; i < NK; ++i) { mbar_init(bars.k_full(i), 1); mbar_init(bars.qk_done(i), 1); }
-    for (int i = 0; i < NV; ++i) mbar_init(bars.v_full(i), 1);
-    for (int i = 0; i < NVEC; ++i) mbar_init(bars.vec_full(i), 1);
-    for (int i = 0; i < NS; ++i) mbar_init(bars.s_free(i), 128);
-    for (int i = 0; i < NP; ++i) mbar_init(bars.p_ready(i), 128);
-    for (int i = 0; i < NPV; ++i) mbar_init(bars.pv_done(i), 1);
-    for (int i = 0; i < NO; ++i) mbar_init(bars.o_empty(i), 128 * C::NDQ);
-    for (int i = 0; i < NSTAT; ++i) mbar_init(bars.stat_full(i), 128);
-    for (int i = 0; i < NM; ++i) mbar_init(bars.m_ready(i), 128);
-    *abort_flag = 0;
+  // One thread per mbarrier (one thread initialising all of them costs a CTA most of a
+  // microsecond before its first copy can be issued).
+  if (tid < C::NUM_BARS) {
+    constexpr int FIRST_S_FREE = 1 + 2 * NK + NV + NVEC, FIRST_PV_DONE = FIRST_S_FREE + NS + NP;
+    constexpr int FIRST_O_EMPTY = FIRST_PV_DONE + NPV, FIRST_STAT = FIRST_O_EMPTY + NO;
+    int count = 1;  // copies and products: one arrival (expect_tx / commit)
+    if (tid >= FIRST_S_FREE && tid < FIRST_PV_DONE) count = 128;                 // s_free, p_ready: a softmax warpgroup
+    else if (tid >= FIRST_O_EMPTY && tid < FIRST_STAT) count = 128 * C::NDQ;      // o_empty: the dequant threads
+    else if (tid >= FIRST_STAT) count = 128;                                      // stat_full, m_ready
+    mbar_init(bars.at(tid), count);
     fence_barrier_init();
   }
+  if (tid == 0) *abort_flag = 0;
   if (tid < 16) reinterpret_cast<volatile uint32_t*>(smem + C::OFF_MAGIC)[tid] = kMagicBits;
   constexpr int PROD_WARP = (NSWG + C::NDQ) * 4;
   constexpr int QK_WARP = PROD_WARP + 1;
   constexpr int PV_WARP = PROD_WARP + 2;
   if (warp == PROD_WARP) {
+    if (lane == 0) { prefetch_tmap(&tm_q); prefetch_tmap(&tm_k); prefetch_tmap(&tm_v); }
     tmem_alloc(smem_u32(const_cast<uint32_t*>(tmem_slot)), TMEM_COLS);
     tmem_relinquish();
     tc_fence_before();
@@ -280,7 +280,6 @@ fused_attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
     // ------------------------------------------------------------------ producer
     // All 32 lanes run the loop and the waits; the elected lane issues the copies.
     if (HELECT) {
-      prefetch_tmap(&tm_q); prefetch_tmap(&tm_k); prefetch_tmap(&tm_v);
       mbar_expect_tx(bars.q_full(), C::Q_BYTES);
       tma_load_2d(smem_base + C::OFF_Q, &tm_q, bars.q_full(), 0, bh * prm.sq_pad + q0);
     }

@@ -195,6 +195,23 @@ def test_prepared_kv_reused_for_three_query_batches_equals_three_full_calls():
         assert call.status()[0] == 0
 
 
+def test_prepared_kv_with_key_order_equals_full_calls():
+    """The same with the long-sequence key order: a full call quantises Q in the launch of the key
+    sort, the split path (prepare_kv, then prepare_q) in a launch of its own; codes, order and
+    outputs must not differ."""
+    from piper_kernels_b200.runtime import AttentionCall
+
+    k = _rand((1, 2, 16500, 128), torch.bfloat16, 43, shift=0.5)
+    v = _rand((1, 2, 16500, 128), torch.bfloat16, 44, shift=1.5)
+    qs = [_rand((1, 2, 333, 128), torch.bfloat16, 80 + i) for i in range(2)]
+    call = AttentionCall("piper", qs[0], k, v, 128 ** -0.5, False, center=True, sort=True).prepare_kv()
+    for q in qs:
+        got = call.requantize_q(q).run().out.clone()
+        want = AttentionCall("piper", q, k, v, 128 ** -0.5, False, center=True, sort=True).fwd().out
+        assert torch.equal(got, want)
+    assert call.status()[0] == 0
+
+
 def test_stalled_wait_gives_up_reports_and_leaves_the_device_usable():
     """The failure path of the fused kernel, exercised without faulting anything: the drill
     instantiation leaves out one K tile's copy and limits every wait to ~0.1 ms.  The wait for the
