@@ -485,7 +485,8 @@ __device__ __forceinline__ uint32_t pack_low_bytes(uint32_t b0, uint32_t b1, uin
 // The work of kThreads threads (`tid` counts them) on NB consecutive 64-row blocks of head `bh`,
 // starting at block `blk0`.  Every thread of the CTA must call it (it holds CTA-wide barriers);
 // `row_max` and `row_scale` are this group's NB * 64 shared-memory slots.
-template <typename T, int D, bool IS_KEY, bool ALIGNED, int NB>
+// FULL: every row of the NB blocks exists (all CTAs of a head but the last): no per-row checks.
+template <typename T, int D, bool IS_KEY, bool ALIGNED, int NB, bool FULL>
 __device__ __forceinline__ void quantize_qk_body(
     const TensorArg& x, const float* __restrict__ mean, const int32_t* __restrict__ order, int8_t* __restrict__ codes,
     float* __restrict__ gscale, float* __restrict__ row_mul, int len, int len_pad, int heads, int per_thread,
@@ -513,14 +514,14 @@ __device__ __forceinline__ void quantize_qk_body(
     for (int p = 0; p < NP; ++p) {
       const int r = (blk0 + b) * kBlockRows + p * RPP + rl;
       src[b][p] = -1;
-      if (r < len) src[b][p] = (IS_KEY && order != nullptr) ? order[static_cast<long long>(bh) * len + r] : r;
+      if (FULL || r < len) src[b][p] = (IS_KEY && order != nullptr) ? order[static_cast<long long>(bh) * len + r] : r;
     }
   }
 #pragma unroll
   for (int b = 0; b < NB; ++b) {
 #pragma unroll
     for (int p = 0; p < NP; ++p) {
-      if (src[b][p] >= 0) load8raw<T, ALIGNED>(xp + static_cast<long long>(src[b][p]) * x.ss + cg * 8, raw[b][p]);
+      if (FULL || src[b][p] >= 0) load8raw<T, ALIGNED>(xp + static_cast<long long>(src[b][p]) * x.ss + cg * 8, raw[b][p]);
       else raw[b][p].u = make_uint4(0u, 0u, 0u, 0u);
     }
   }
@@ -535,7 +536,7 @@ __device__ __forceinline__ void quantize_qk_body(
       float2 v[4];
       unpack8<T>(raw[b][p], v);
       float m = 0.f;
-      if (src[b][p] >= 0) {
+      if (FULL || src[b][p] >= 0) {
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
           if (IS_KEY) v[i] = __fadd2_rn(v[i], neg_mu[i]);
@@ -575,10 +576,10 @@ __device__ __forceinline__ void quantize_qk_body(
     const float s = __fadd_rn(__fdiv_rn(g, 127.f), 1e-7f);
     row_scale[tid] = make_float2(s, __fdiv_rn(1.f, s));
     const int gr = blk * kBlockRows + r;
-    if (gr < len_pad) {
+    if (FULL || gr < len_pad) {
       row_mul[static_cast<long long>(bh) * len_pad + gr] = s * mul;
       if (per_thread) {
-        if (gr < len) gscale[static_cast<long long>(bh) * groups_per_head + gr] = s;
+        if (FULL || gr < len) gscale[static_cast<long long>(bh) * groups_per_head + gr] = s;
       } else if (IS_KEY) {
         if (r == 0) gscale[static_cast<long long>(bh) * groups_per_head + blk] = s;
       } else if ((r & 31) == 0) {
@@ -594,7 +595,7 @@ __device__ __forceinline__ void quantize_qk_body(
     for (int p = 0; p < NP; ++p) {
       const int lr = b * kBlockRows + p * RPP + rl;
       const int r = blk0 * kBlockRows + lr;
-      if (r >= len_pad) continue;
+      if (!FULL && r >= len_pad) continue;
       const float2 sc = row_scale[lr];
       uint32_t c[8];
       if (HOLD) {
@@ -602,7 +603,7 @@ __device__ __forceinline__ void quantize_qk_body(
       } else {
         float2 v[4];
         unpack8<T>(raw[b][p], v);  // padding rows hold zeros and stay zero
-        if (IS_KEY && src[b][p] >= 0) {
+        if (IS_KEY && (FULL || src[b][p] >= 0)) {
 #pragma unroll
           for (int i = 0; i < 4; ++i) v[i] = __fadd2_rn(v[i], neg_mu[i]);
         }
@@ -623,9 +624,16 @@ __global__ void __launch_bounds__(kThreads, 3) quantize_qk_kernel(
   // block with the unpacked values held, most of all for rows gathered through the key order
   __shared__ float row_max[kQuantBlocks * kBlockRows];
   __shared__ float2 row_scale[kQuantBlocks * kBlockRows];  // scale and its reciprocal
-  quantize_qk_body<T, D, IS_KEY, ALIGNED, kQuantBlocks>(x, mean, order, codes, gscale, row_mul, len, len_pad, heads,
-                                                        per_thread, groups_per_head, mul, blockIdx.y,
-                                                        blockIdx.x * kQuantBlocks, threadIdx.x, row_max, row_scale);
+  const int blk0 = blockIdx.x * kQuantBlocks;
+  if ((blk0 + kQuantBlocks) * kBlockRows <= len) {
+    quantize_qk_body<T, D, IS_KEY, ALIGNED, kQuantBlocks, true>(x, mean, order, codes, gscale, row_mul, len, len_pad, heads,
+                                                                per_thread, groups_per_head, mul, blockIdx.y, blk0,
+                                                                threadIdx.x, row_max, row_scale);
+  } else {
+    quantize_qk_body<T, D, IS_KEY, ALIGNED, kQuantBlocks, false>(x, mean, order, codes, gscale, row_mul, len, len_pad, heads,
+                                                                 per_thread, groups_per_head, mul, blockIdx.y, blk0,
+                                                                 threadIdx.x, row_max, row_scale);
+  }
 }
 
 // The key order of every head (CTAs [0, n_heads): one 1024-thread sort each, a few CTAs that
@@ -647,9 +655,17 @@ __global__ void __launch_bounds__(kSortThreads) sort_and_quantize_q_kernel(
     const int c = blockIdx.x - n_heads;
     const int bh = c / q_ctas_per_head, group = threadIdx.x / kThreads;
     const int blk0 = (c % q_ctas_per_head) * GROUPS + group;
-    quantize_qk_body<T, D, false, ALIGNED, 1>(q, nullptr, nullptr, codes, gscale, row_mul, len, len_pad, heads, per_thread,
-                                              groups_per_head, mul, bh, blk0, threadIdx.x % kThreads, row_max[group],
-                                              row_scale[group]);
+    // the whole CTA takes one path (it holds CTA-wide barriers): the checked one unless all four blocks are full
+    const int cta_last_row = ((c % q_ctas_per_head) * GROUPS + GROUPS) * kBlockRows;
+    if (cta_last_row <= len) {
+      quantize_qk_body<T, D, false, ALIGNED, 1, true>(q, nullptr, nullptr, codes, gscale, row_mul, len, len_pad, heads,
+                                                      per_thread, groups_per_head, mul, bh, blk0, threadIdx.x % kThreads,
+                                                      row_max[group], row_scale[group]);
+    } else {
+      quantize_qk_body<T, D, false, ALIGNED, 1, false>(q, nullptr, nullptr, codes, gscale, row_mul, len, len_pad, heads,
+                                                       per_thread, groups_per_head, mul, bh, blk0, threadIdx.x % kThreads,
+                                                       row_max[group], row_scale[group]);
+    }
   }
 }
 
@@ -658,11 +674,11 @@ __global__ void __launch_bounds__(kSortThreads) sort_and_quantize_q_kernel(
 // is a K-major B operand of the PV product.  PIPER: per-key INT8 of (v - mean), plus
 // log2(scale) and 1/scale per key.  SAGE: per-channel E4M3.
 // ---------------------------------------------------------------------------------------
-template <typename T, int D, bool SAGE, bool ALIGNED>
-__global__ void __launch_bounds__(kThreads, 3) quantize_v_kernel(
-    TensorArg v, const float* __restrict__ v_mean_or_scale, const int32_t* __restrict__ order,
+template <typename T, int D, bool SAGE, bool ALIGNED, bool FULL>
+__device__ __forceinline__ void quantize_v_body(
+    const TensorArg& v, const float* __restrict__ v_mean_or_scale, const int32_t* __restrict__ order,
     uint8_t* __restrict__ codes_t, float* __restrict__ v_scale, float* __restrict__ col_add,
-    float* __restrict__ col_inv, int sk, int sk_pad, int heads) {
+    float* __restrict__ col_inv, int sk, int sk_pad, int heads, uint32_t* tile) {
   constexpr int TPR = D / 8;
   constexpr int RPP = kThreads / TPR;
   constexpr int NP = kBlockRows / RPP;  // adjacent keys per thread and block: 4 (head_dim 128) or 2 (64)
@@ -673,7 +689,6 @@ __global__ void __launch_bounds__(kThreads, 3) quantize_v_kernel(
   // so it writes one (half) word per feature and block.  The word position is rotated by the
   // feature group so that the 16 (8) threads that hold the same keys of different feature
   // groups hit different banks.
-  __shared__ __align__(16) uint32_t tile[D * WPR];
   const int bh = blockIdx.y, blk0 = blockIdx.x * NB;
   const int cg = threadIdx.x % TPR, rl = threadIdx.x / TPR;
   const T* vp = static_cast<const T*>(head_ptr(v, bh, heads, sizeof(T)));
@@ -691,14 +706,14 @@ __global__ void __launch_bounds__(kThreads, 3) quantize_v_kernel(
     for (int p = 0; p < NP; ++p) {
       const int r = (blk0 + b) * kBlockRows + rl * NP + p;
       src[b][p] = -1;
-      if (r < sk) src[b][p] = (!SAGE && order != nullptr) ? order[static_cast<long long>(bh) * sk + r] : r;
+      if (FULL || r < sk) src[b][p] = (!SAGE && order != nullptr) ? order[static_cast<long long>(bh) * sk + r] : r;
     }
   }
 #pragma unroll
   for (int b = 0; b < NB; ++b) {
 #pragma unroll
     for (int p = 0; p < NP; ++p) {
-      if (src[b][p] >= 0) load8raw<T, ALIGNED>(vp + static_cast<long long>(src[b][p]) * v.ss + cg * 8, raw[b][p]);
+      if (FULL || src[b][p] >= 0) load8raw<T, ALIGNED>(vp + static_cast<long long>(src[b][p]) * v.ss + cg * 8, raw[b][p]);
       else raw[b][p].u = make_uint4(0u, 0u, 0u, 0u);
     }
   }
@@ -715,7 +730,7 @@ __global__ void __launch_bounds__(kThreads, 3) quantize_v_kernel(
       uint32_t c[8];  // word whose low byte is the code of (key p, feature i)
       if (!SAGE) {
         float m = 0.f;
-        if (r < sk) {
+        if (FULL || r < sk) {
 #pragma unroll
           for (int i = 0; i < 4; ++i) {
             x[i] = __fadd2_rn(x[i], make_float2(-aux[2 * i], -aux[2 * i + 1]));
@@ -725,9 +740,9 @@ __global__ void __launch_bounds__(kThreads, 3) quantize_v_kernel(
         m = group_max<TPR>(m);
         const float s = __fadd_rn(__fdiv_rn(m, 127.f), 1e-7f);
         const float rs = __fdiv_rn(1.f, s);
-        if (cg == 0 && r < sk_pad) {
+        if (cg == 0 && (FULL || r < sk_pad)) {
           const long long o = static_cast<long long>(bh) * sk_pad + r;
-          if (r < sk) {
+          if (FULL || r < sk) {
             v_scale[static_cast<long long>(bh) * sk + r] = s;
             col_add[o] = log2f(s);
             col_inv[o] = rs;
@@ -738,7 +753,7 @@ __global__ void __launch_bounds__(kThreads, 3) quantize_v_kernel(
         }
         round_i8_row8(x, s, rs, c);
       } else {
-        if (cg == 0 && r < sk_pad) col_add[static_cast<long long>(bh) * sk_pad + r] = (r < sk) ? 0.f : -INFINITY;
+        if (cg == 0 && (FULL || r < sk_pad)) col_add[static_cast<long long>(bh) * sk_pad + r] = (FULL || r < sk) ? 0.f : -INFINITY;
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
           c[2 * i] = __nv_cvt_float_to_fp8(__fdiv_rn(x[i].x, aux[2 * i]), __NV_SATFINITE, __NV_E4M3);
@@ -766,9 +781,23 @@ __global__ void __launch_bounds__(kThreads, 3) quantize_v_kernel(
   const int valid_quads = min(NB * kBlockRows, sk_pad - blk0 * kBlockRows) / 16;  // the last CTA may hold one block
   for (int idx = threadIdx.x; idx < D * (WPR / 4); idx += kThreads) {
     const int d = idx / (WPR / 4), g = idx % (WPR / 4);
-    if (g >= valid_quads) continue;
+    if (!FULL && g >= valid_quads) continue;
     const uint4 val = *reinterpret_cast<const uint4*>(tile + d * WPR + (4 * g + 4 * (d / 8)) % WPR);
     *reinterpret_cast<uint4*>(codes_t + (static_cast<long long>(bh) * D + d) * sk_pad + blk0 * kBlockRows + g * 16) = val;
+  }
+}
+
+template <typename T, int D, bool SAGE, bool ALIGNED>
+__global__ void __launch_bounds__(kThreads, 3) quantize_v_kernel(
+    TensorArg v, const float* __restrict__ v_mean_or_scale, const int32_t* __restrict__ order,
+    uint8_t* __restrict__ codes_t, float* __restrict__ v_scale, float* __restrict__ col_add,
+    float* __restrict__ col_inv, int sk, int sk_pad, int heads) {
+  __shared__ __align__(16) uint32_t tile[D * kQuantBlocks * kBlockRows / 4];
+  // every key of this CTA's blocks exists (all CTAs of a head but the last): no per-key checks
+  if ((static_cast<int>(blockIdx.x) + 1) * kQuantBlocks * kBlockRows <= sk) {
+    quantize_v_body<T, D, SAGE, ALIGNED, true>(v, v_mean_or_scale, order, codes_t, v_scale, col_add, col_inv, sk, sk_pad, heads, tile);
+  } else {
+    quantize_v_body<T, D, SAGE, ALIGNED, false>(v, v_mean_or_scale, order, codes_t, v_scale, col_add, col_inv, sk, sk_pad, heads, tile);
   }
 }
 
