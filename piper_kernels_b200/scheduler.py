@@ -79,9 +79,11 @@ class HostAttentionPipeline:
     """Attention on inputs and outputs that live in pinned host memory.
 
     Heads are independent, so the flat (batch x heads) axis is cut into chunks (see
-    :func:`plan_chunks`) and four CUDA streams overlap: the upload of chunk i+1, its quantisation
+    :func:`plan_chunks`) and five CUDA streams overlap: the upload of chunk i+1, its quantisation
     prepass (on a high-priority stream, so that its short kernels get SMs as soon as blocks of the
-    running fused kernel retire), the fused kernel of chunk i and the download of chunk i-1.
+    running fused kernel retire), the fused kernel of chunk i and the download of chunk i-1.  The
+    fused kernels alternate between two streams: a chunk's CTAs fill whole waves of SMs only by
+    chance, and the next chunk's kernel then starts on the SMs its last, partial wave leaves idle.
     Device staging buffers (two slots per tensor) and the prepared calls (one per slot and chunk
     size, each with its workspace and output) are allocated once and re-used.
 
@@ -95,6 +97,7 @@ class HostAttentionPipeline:
         self.up = torch.cuda.Stream(self.device)
         self.down = torch.cuda.Stream(self.device)
         self.prep = torch.cuda.Stream(self.device, priority=-1)
+        self.run_b = torch.cuda.Stream(self.device)
         self._slots = None
         self._key = None
         self._calls = {}
@@ -147,7 +150,7 @@ class HostAttentionPipeline:
         fo = out_host.view(flat, *out_host.shape[2:])
         slots = self._staging(q_host, k_host, v_host)
         main = torch.cuda.current_stream(self.device)
-        for s in (self.up, self.down, self.prep):
+        for s in (self.up, self.down, self.prep, self.run_b):
             s.wait_stream(main)
         start = 0
         for i, n in enumerate(plan_chunks(flat, self.heads_per_chunk)):
@@ -169,19 +172,21 @@ class HostAttentionPipeline:
                     call.prepare()
                 prepared = torch.cuda.Event()
                 prepared.record(self.prep)
-            main.wait_event(prepared)
-            if call.drained is not None:
-                main.wait_event(call.drained)  # the download of this call's previous result has finished
-            if not copy_only:
-                call.run()
-            slot["free"] = torch.cuda.Event()
-            slot["free"].record(main)
+            run = main if i % 2 == 0 else self.run_b
+            with torch.cuda.stream(run):
+                run.wait_event(prepared)
+                if call.drained is not None:
+                    run.wait_event(call.drained)  # the download of this call's previous result has finished
+                if not copy_only:
+                    call.run()
+                slot["free"] = torch.cuda.Event()
+                slot["free"].record(run)
             with torch.cuda.stream(self.down):
                 self.down.wait_event(slot["free"])
                 fo[sl].copy_(call.out[0], non_blocking=True)
                 call.drained = torch.cuda.Event()
                 call.drained.record(self.down)
-        for s in (self.down, self.up, self.prep):
+        for s in (self.down, self.up, self.prep, self.run_b):
             main.wait_stream(s)
         return out_host
 
