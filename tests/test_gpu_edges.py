@@ -65,6 +65,65 @@ def test_ragged_lengths_piper_and_sage(sq, sk, d):
     _check16(_np(pk.sage_attention_2pp(q, k, v)), out, torch.float16)
 
 
+def _random_case(seed):
+    rng = np.random.default_rng(seed)
+    d = int(rng.choice([64, 128]))
+    b, h = int(rng.integers(1, 3)), int(rng.integers(1, 4))
+    sk = int(rng.integers(1, 700))
+    causal = bool(rng.integers(0, 4) == 0)
+    sq = sk if causal else int(rng.integers(1, 500))
+    dtype = torch.float16 if rng.integers(0, 2) else torch.bfloat16
+    return d, b, h, sq, sk, causal, dtype
+
+
+@pytest.mark.parametrize("seed", range(12))
+def test_random_shapes_codes_bit_exact_and_outputs_in_tolerance(seed):
+    """Seeded random problems (ragged lengths, odd numbers of 64-row blocks, several heads, both
+    operators and granularities): every code, scale and mean-dependent quantity the prepass
+    leaves in the workspace equals the oracle's bit for bit, and the FP32 output is within the
+    gate.  The quantizers take a check-free path for CTAs whose rows all exist and a checked one
+    for the last CTA of a head; random lengths hit both."""
+    from piper_kernels_b200.runtime import AttentionCall
+
+    d, b, h, sq, sk, causal, dtype = _random_case(1000 + seed)
+    q = _rand((b, h, sq, d), dtype, 3 * seed + 1)
+    k = _rand((b, h, sk, d), dtype, 3 * seed + 2, shift=0.3)
+    v = _rand((b, h, sk, d), dtype, 3 * seed + 3, shift=-0.7)
+    qf, kf, vf = _np(q), _np(k), _np(v)
+    for algo, gran in (("piper", "per_warp"), ("piper", "per_thread"), ("sage2pp", "per_thread"), ("sage2pp", "per_warp")):
+        if algo == "piper":
+            center = not causal
+            prep = oracle.piper_prepare_oracle(qf, kf, vf, center_value=center, qk_quantization=gran)
+            call = AttentionCall("piper", q, k, v, d ** -0.5, causal, center=center, gran=gran, out_dtype=torch.float32,
+                                 k_mean=prep["k_mean"].reshape(b * h, d), v_mean=prep["v_mean"].reshape(b * h, d))
+            want = oracle.piper_attention_oracle(qf, kf, vf, d ** -0.5, causal, center_value=center, qk_quantization=gran)
+        else:
+            prep = oracle.sage_prepare_oracle(qf, kf, vf, qk_quantization=gran)
+            call = AttentionCall("sage2pp", q, k, v, d ** -0.5, causal, gran=gran, out_dtype=torch.float32,
+                                 k_mean=prep["k_mean"].reshape(b * h, d))
+            want = oracle.sage_attention_2pp_oracle(qf, kf, vf, d ** -0.5, causal, qk_quantization=gran)
+        call.prepare().run()
+        torch.cuda.synchronize()
+        assert call.status()[0] == 0
+        vw = call.views
+        bh = b * h
+        qc = call.view("q_codes", torch.int8, (bh, vw.sq_pad, d)).cpu().numpy()
+        kc = call.view("k_codes", torch.int8, (bh, vw.sk_pad, d)).cpu().numpy()
+        vt = call.view("v_codes_t", torch.uint8, (bh, d, vw.sk_pad)).cpu().numpy()
+        assert np.array_equal(qc[:, :sq], prep["q_codes"].reshape(bh, sq, d)) and not qc[:, sq:].any()
+        assert np.array_equal(kc[:, :sk], prep["k_codes"].reshape(bh, sk, d)) and not kc[:, sk:].any()
+        want_v = prep["v_codes"].reshape(bh, sk, d)
+        assert np.array_equal(vt.transpose(0, 2, 1)[:, :sk].view(want_v.dtype), want_v) and not vt[:, :, sk:].any()
+        qg = prep["q_group_scale"].reshape(bh, -1)
+        kg = prep["k_group_scale"].reshape(bh, -1)
+        assert np.array_equal(call.view("q_group_scale", torch.float32, qg.shape).cpu().numpy(), qg)
+        assert np.array_equal(call.view("k_group_scale", torch.float32, kg.shape).cpu().numpy(), kg)
+        out = _np(call.out)
+        assert np.isfinite(out).all()
+        assert np.abs(out - want).max() <= MAX_ABS, (seed, algo, gran, d, b, h, sq, sk, causal)
+        assert cosine(out, want) >= MIN_COS
+
+
 @pytest.mark.parametrize("s", [1, 64, 100, 257, 1000])
 def test_causal_lengths(s):
     q = _rand((2, 1, s, 128), torch.bfloat16, 400 + s)
