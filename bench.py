@@ -472,8 +472,9 @@ def ours_arm(args, w, rank, local_rank, world):
         kwargs = dict(is_causal=w.causal, center_value=w.center) if w.op == "piper" else dict(is_causal=w.causal)
         fn = pk.piper_attention if w.op == "piper" else pk.sage_attention_2pp
         local_heads = q.shape[0] * q.shape[1]
-        chunk = max(1, min(4, local_heads // 4))  # 8-head chunks measured slower (32.5 against 31.4 ms per c4 step)
-        pipe = HostAttentionPipeline(dev, heads_per_chunk=chunk)
+        # measured per c4 step: chunks of 2 heads with 4 staging slots 29.0 ms; 4 heads / 2 slots 29.9; 8 heads 32.5
+        chunk = max(1, min(2, local_heads // 4))
+        pipe = HostAttentionPipeline(dev, heads_per_chunk=chunk, slots=4)
 
         def e2e_step():
             pipe(fn, hq, hk, hv, hout, **kwargs)
@@ -491,7 +492,7 @@ def ours_arm(args, w, rank, local_rank, world):
                "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                "copy_only_ms_per_step": copy_ms, "copy_only_gbs_per_rank": (h2d + d2h) / (copy_ms * 1e-3) / 1e9,
                "frac_of_copy_ceiling": copy_ms / e2e_ms,
-               "api": f"scheduler.HostAttentionPipeline, ramped chunks of up to {chunk} heads, pinned host buffers"}
+               "api": f"scheduler.HostAttentionPipeline, chunks of up to {chunk} heads, 4 staging slots, pinned host buffers"}
 
     quality = None
     if args.quality and rank == 0:

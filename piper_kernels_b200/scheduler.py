@@ -84,16 +84,17 @@ class HostAttentionPipeline:
     running fused kernel retire), the fused kernel of chunk i and the download of chunk i-1.  The
     fused kernels alternate between two streams: a chunk's CTAs fill whole waves of SMs only by
     chance, and the next chunk's kernel then starts on the SMs its last, partial wave leaves idle.
-    Device staging buffers (two slots per tensor) and the prepared calls (one per slot and chunk
+    Device staging buffers (``slots`` per tensor) and the prepared calls (one per slot and chunk
     size, each with its workspace and output) are allocated once and re-used.
 
     ``op`` is the public function whose semantics are wanted, ``piper_attention`` or
     ``sage_attention_2pp``; keyword arguments are the ones that function takes.
     """
 
-    def __init__(self, device, *, heads_per_chunk: int = 4):
+    def __init__(self, device, *, heads_per_chunk: int = 2, slots: int = 4):
         self.device = torch.device(device)
         self.heads_per_chunk = int(heads_per_chunk)
+        self.n_slots = max(2, int(slots))  # staging slots: uploads run this many chunks ahead of the fused kernels
         self.up = torch.cuda.Stream(self.device)
         self.down = torch.cuda.Stream(self.device)
         self.prep = torch.cuda.Stream(self.device, priority=-1)
@@ -107,7 +108,7 @@ class HostAttentionPipeline:
         if self._key != key:
             n = self.heads_per_chunk
             mk = lambda t: torch.empty((n, *t.shape[2:]), dtype=t.dtype, device=self.device)  # noqa: E731
-            self._slots = [{"q": mk(q), "k": mk(k), "v": mk(v), "free": None} for _ in range(2)]
+            self._slots = [{"q": mk(q), "k": mk(k), "v": mk(v), "free": None} for _ in range(self.n_slots)]
             self._key = key
             self._calls = {}
         return self._slots
@@ -156,8 +157,8 @@ class HostAttentionPipeline:
         for i, n in enumerate(plan_chunks(flat, self.heads_per_chunk)):
             sl = slice(start, start + n)
             start += n
-            slot = slots[i % 2]
-            call = self._call(op, i % 2, n, kwargs)
+            slot = slots[i % self.n_slots]
+            call = self._call(op, i % self.n_slots, n, kwargs)
             with torch.cuda.stream(self.up):
                 if slot["free"] is not None:
                     self.up.wait_event(slot["free"])  # the fused kernel that read this slot has finished
@@ -192,6 +193,6 @@ class HostAttentionPipeline:
 
 
 def attention_from_host(op, q_host: torch.Tensor, k_host: torch.Tensor, v_host: torch.Tensor,
-                        out_host: torch.Tensor, device, *, heads_per_chunk: int = 4, **kwargs) -> torch.Tensor:
+                        out_host: torch.Tensor, device, *, heads_per_chunk: int = 2, slots: int = 4, **kwargs) -> torch.Tensor:
     """One-shot form of :class:`HostAttentionPipeline` (allocates the staging buffers per call)."""
-    return HostAttentionPipeline(device, heads_per_chunk=heads_per_chunk)(op, q_host, k_host, v_host, out_host, **kwargs)
+    return HostAttentionPipeline(device, heads_per_chunk=heads_per_chunk, slots=slots)(op, q_host, k_host, v_host, out_host, **kwargs)
