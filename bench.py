@@ -460,7 +460,7 @@ def ours_arm(args, w, rank, local_rank, world):
     # prepass, fused kernel and download overlap on four streams (heads are independent)
     e2e = None
     if not args.no_e2e:
-        from piper_kernels_b200.scheduler import HostAttentionPipeline
+        from piper_kernels_b200.scheduler import HostAttentionPipeline, suggest_heads_per_chunk
 
         hq = q.contiguous().cpu().pin_memory()
         if w.name == "c5":  # keep the interleaved K/V layout (sequence stride 2*D) in host memory too
@@ -472,8 +472,7 @@ def ours_arm(args, w, rank, local_rank, world):
         kwargs = dict(is_causal=w.causal, center_value=w.center) if w.op == "piper" else dict(is_causal=w.causal)
         fn = pk.piper_attention if w.op == "piper" else pk.sage_attention_2pp
         local_heads = q.shape[0] * q.shape[1]
-        # measured per c4 step: chunks of 2 heads with 4 staging slots 29.0 ms; 4 heads / 2 slots 29.9; 8 heads 32.5
-        chunk = max(1, min(2, local_heads // 4))
+        chunk = suggest_heads_per_chunk(w.ops(1), local_heads)
         pipe = HostAttentionPipeline(dev, heads_per_chunk=chunk, slots=4)
 
         def e2e_step():
