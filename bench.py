@@ -454,6 +454,16 @@ def ours_arm(args, w, rank, local_rank, world):
     prep_each = timed_each(lambda: call.prepare(), max(args.steps, 5), sync)
     status = call.status()
     out_prepared = call.out.clone() if args.quality else None
+    # the same whole call (prepass + fused kernel) replayed from a CUDA graph: what a caller who
+    # captures the launch-bound small problems gets (c1: 8 launches of 54 us in a 100 us eager step)
+    graph_ms = None
+    try:
+        from piper_kernels_b200.runtime import GraphedAttention
+        graphed = GraphedAttention(call)
+        graph_ms = max_over_ranks(timed(graphed.replay, args.steps, sync, barrier))
+        del graphed
+    except Exception as e:  # noqa: BLE001 - a side measurement must not fail the run
+        print(f"graph replay not measured: {e}", file=sys.stderr)
     del call
 
     # end to end from pinned host memory through the public host entry point: per-head-chunk upload,
@@ -571,6 +581,7 @@ def ours_arm(args, w, rank, local_rank, world):
         "data": "synthetic", "config": workload_config(w, world, args.scaling, heads_per_rank), "clocks": clocks, "e2e": e2e,
         "gpu_launches": (prepass_launches + 1 + (1 if key_split else 0)) * args.steps, "roofline": roofline, "cpu_baseline": cpu_baseline,
         "roofline_prepass": roofline_prepass, "device_status": status[0],
+        "graph_replay": None if graph_ms is None else {"ms_per_step": graph_ms, "value": total_ops / (graph_ms * 1e-3) / 1e12, "unit": UNIT},
         "per_gpu_value": value / world,
         "value_full_rectangle": (4.0 * total_heads * w.q_len * w.kv_len * w.head_dim / (ms * 1e-3) / 1e12) if w.causal else None,
         "quality": quality,

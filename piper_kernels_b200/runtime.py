@@ -116,3 +116,30 @@ class AttentionCall:
         pc = raw[128 * 64 * 4: 128 * 64 * 5].reshape(128, 64)
         o = raw[128 * 64 * 5:].view(np.int32).reshape(128, d)
         return s, pc, o
+
+
+class GraphedAttention:
+    """prepare + run of an :class:`AttentionCall` captured once in a CUDA graph and replayed.
+
+    A small problem's eight launches take longer to issue than to run (c1: 54 us of kernels in a
+    127 us step); the library allocates nothing and never synchronises, so the whole call can be
+    captured.  The call's q/k/v tensors are the graph's inputs (copy new data into them in place)
+    and ``call.out`` its output.  The first launches on a device set function attributes and map
+    the pinned fault word, so the call runs once eagerly before the capture."""
+
+    def __init__(self, call: AttentionCall):
+        self.call = call
+        dev = call.q.device
+        side = torch.cuda.Stream(dev)
+        side.wait_stream(torch.cuda.current_stream(dev))
+        with torch.cuda.stream(side):
+            call.fwd()
+        torch.cuda.current_stream(dev).wait_stream(side)
+        torch.cuda.synchronize(dev)
+        self.graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(self.graph):
+            call.fwd()
+
+    def replay(self):
+        self.graph.replay()
+        return self.call.out

@@ -271,6 +271,27 @@ def test_prepared_kv_with_key_order_equals_full_calls():
     assert call.status()[0] == 0
 
 
+def test_whole_call_replays_from_a_cuda_graph():
+    """The library allocates nothing and never synchronises: prepass + fused kernel (with the key
+    split and its merge launch for piper) are captured in a CUDA graph once and replayed on new
+    inputs written into the same tensors; results equal the eager operator's bit for bit."""
+    from piper_kernels_b200.runtime import AttentionCall, GraphedAttention
+
+    for algo in ("piper", "sage2pp"):
+        q = _rand((1, 8, 1024, 64), torch.float16, 91)
+        k = _rand((1, 8, 1024, 64), torch.float16, 92)
+        v = _rand((1, 8, 1024, 64), torch.float16, 93)
+        graphed = GraphedAttention(AttentionCall(algo, q, k, v, 64 ** -0.5, False))
+        for seed in (94, 97):
+            q.copy_(_rand(q.shape, q.dtype, seed))
+            k.copy_(_rand(k.shape, k.dtype, seed + 1, shift=0.5))
+            v.copy_(_rand(v.shape, v.dtype, seed + 2))
+            got = graphed.replay().clone()
+            want = pk.piper_attention(q, k, v, center_value=False) if algo == "piper" else pk.sage_attention_2pp(q, k, v)
+            assert torch.equal(got, want)
+        assert graphed.call.status()[0] == 0
+
+
 def test_stalled_wait_gives_up_reports_and_leaves_the_device_usable():
     """The failure path of the fused kernel, exercised without faulting anything: the drill
     instantiation leaves out one K tile's copy and limits every wait to ~0.1 ms.  The wait for the
