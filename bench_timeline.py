@@ -41,7 +41,8 @@ def summarize(tr: np.ndarray, n_tiles: int, nswg: int) -> str:
     4 scores in registers, 2 tile max known / score buffer released, 5 codes computed,
     6 probability buffer free, 7 probabilities stored, 3 published; dequant 0 start, 1 rescaled,
     2 first chunk loaded, 4 early chunks folded, 7 next statistics done, 5 next tile's product
-    complete, 6 all chunks folded, 3 buffer released; issue warps 0 start, 1 operands
+    complete, 6 all chunks folded, 3 buffer released (when the fold starts from the top of the tile: 0 start,
+    7 statistics done, 5 product complete, 1 rescaled, 2 first chunk loaded, 6, 3; slot 4 stays empty); issue warps 0 start, 1 operands
     ready, 2 issued; producer 0 start, 1 K stage free, 2 copies issued."""
     n = min(n_tiles, tr.shape[1])
     t0 = tr[tr > 0].min()
@@ -58,9 +59,14 @@ def summarize(tr: np.ndarray, n_tiles: int, nswg: int) -> str:
         else:
             lines.append(f"softmax{w}: wait {d(x, 0, 1):.0f} | pass 1 {d(x, 1, 2):.0f} | pass 2 + publish {d(x, 2, 3):.0f} | per own tile {np.mean(np.diff(x[:, 0])):.0f}")
     x = tr[nswg, lo:hi]
-    lines.append(f"dequant : rescale {d(x, 0, 1):.0f} | first chunk {d(x, 1, 2):.0f} | early chunks {d(x, 2, 4):.0f} | "
-                 f"next tile's statistics {d(x, 4, 7):.0f} | next tile's product wait {d(x, 7, 5):.0f} | remaining chunks {d(x, 5, 6):.0f} | "
-                 f"release {d(x, 6, 3):.0f} | per tile {np.mean(np.diff(x[:, 0])):.0f}")
+    top = x[:, 4].min() < 0  # the fold starts from the top of the tile: statistics and product wait come first
+    if top:
+        lines.append(f"dequant : statistics {d(x, 0, 7):.0f} | product wait {d(x, 7, 5):.0f} | rescale {d(x, 5, 1):.0f} | first chunk {d(x, 1, 2):.0f} | "
+                     f"other chunks {d(x, 2, 6):.0f} | release {d(x, 6, 3):.0f} | per tile {np.mean(np.diff(x[:, 0])):.0f}")
+    else:
+        lines.append(f"dequant : rescale {d(x, 0, 1):.0f} | first chunk {d(x, 1, 2):.0f} | early chunks {d(x, 2, 4):.0f} | "
+                     f"next tile's statistics {d(x, 4, 7):.0f} | next tile's product wait {d(x, 7, 5):.0f} | remaining chunks {d(x, 5, 6):.0f} | "
+                     f"release {d(x, 6, 3):.0f} | per tile {np.mean(np.diff(x[:, 0])):.0f}")
     for r, name in ((nswg + 1, "S issue "), (nswg + 2, "PV issue")):
         x = tr[r, lo:hi]
         lines.append(f"{name}: wait {d(x, 0, 1):.0f} | issue {d(x, 1, 2):.0f} | per tile {np.mean(np.diff(x[:, 0])):.0f}")
@@ -69,7 +75,7 @@ def summarize(tr: np.ndarray, n_tiles: int, nswg: int) -> str:
         lines.append(f"producer: wait K stage {d(x, 0, 1):.0f} | wait V stage + issue copies {d(x, 1, 2):.0f} | per tile {np.mean(np.diff(x[:, 0])):.0f}")
     own = np.arange(n) % nswg
     p_done = tr[own, np.arange(n), 3]
-    lines.append(f"P published -> PV issued {np.mean(tr[nswg + 2, lo:hi, 2] - p_done[lo:hi]):.0f} | PV issued -> fold begins {np.mean(tr[nswg, lo:hi, 0] - tr[nswg + 2, lo:hi, 2]):.0f} | "
+    lines.append(f"P published -> PV issued {np.mean(tr[nswg + 2, lo:hi, 2] - p_done[lo:hi]):.0f} | PV issued -> fold begins {np.mean(tr[nswg, lo:hi, 5 if top else 0] - tr[nswg + 2, lo:hi, 2]):.0f} | "
                  f"S issued -> softmax picks it up {np.mean(tr[own, np.arange(n), 1][lo:hi] - tr[nswg + 1, lo:hi, 2]):.0f}")
     return "\n".join(lines)
 

@@ -111,6 +111,12 @@ struct Cfg {
   // 1-2 % faster with lane 0 running the loop alone.
   static constexpr bool PRODUCER_CONVERGED = ALGO == kSage;
   static constexpr int PRODUCER_SLEEP_NS = ALGO == kPiper ? 500 : 0;
+  // Where the dequant warpgroup evaluates a tile's factors and waits for its product: at the top
+  // of the tile (the eight chunks of the fold are then one straight-line block that the compiler
+  // schedules as a whole: 6-7 % faster for piper, where the dequant sets the period), or one tile
+  // ahead in the middle of the previous tile's fold with the first chunk's load in flight across
+  // the tile boundary (1 % faster for sage at head_dim 64, where the softmax warpgroups set it).
+  static constexpr bool FOLD_FROM_TILE_TOP = !(ALGO == kSage && D == 64);
   // setmaxnreg only moves registers between the warps of the CTA: an increase waits (without a time
   // limit) until other warps have released enough, so the budgets must fit what the CTA was launched with.
   static_assert((NSWG * REG_SM + NDQ * REG_DQ + REG_HELPER) * 128 <= THREADS * LAUNCH_REGS,
@@ -589,20 +595,22 @@ fused_attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
       }
       return true;
     };
-    // The partial is read CH columns at a time; the next chunk's load is always in flight while
-    // the current one is folded, across tile boundaries too: the first chunk of tile j+1 is
-    // requested before the last chunk of tile j is folded.  Each chunk is re-armed once read.
+    // The partial is read CH columns at a time; the next chunk's load is in flight while the
+    // current one is folded, and each chunk is re-armed once read.  FOLD_FROM_TILE_TOP: the
+    // tile's factors are evaluated and its product awaited before its first chunk is requested.
+    // Otherwise both happen one tile ahead (at chunk STAT_AT / NEXT_AT of the previous tile) and
+    // the first chunk of tile j+1 is requested before the last chunk of tile j is folded.
     constexpr int NCH = DH / CH;
     static_assert(NCH >= 2, "the next tile's product is waited for before the last chunk");
     constexpr int STAT_AT = 1;  // chunk after which the next tile's factors are evaluated
-    // ... and the next tile's product awaited.  Any later chunk measured 4-6 % slower: the folds that
-    // then run while that product executes slow down by as much as the wait shortens.
+    // ... and the next tile's product awaited.  Which chunk makes no difference as long as the two
+    // stay together: every wait splits the unrolled fold into another block (6-7 % per split).
     constexpr int NEXT_AT = 1;
     uint32_t obuf[2][CH];
     const float2 neg_magic2 = make_float2(-kMagic, -kMagic);
     uint32_t armv[16];
     load_arm_block(smem_base + C::OFF_MAGIC, armv);
-    if (n_tiles > 0) {
+    if (!C::FOLD_FROM_TILE_TOP && n_tiles > 0) {
       ok = advance_stats(0);
       ok = ok && WARP_ALL(mbar_wait_bounded(bars.pv_done(0), 0, abort_flag, W_DQ_O, kLimit));
       if (ok) {
@@ -612,8 +620,17 @@ fused_attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
     }
     for (int j = 0; ok && j < n_tiles; ++j) {
       PK_STAMP(NSWG, j, 0);
-      ow = ow_n; c = c_n;
       const uint32_t o_addr = lane_addr + C::COL_O + (j % NO) * D + col0;
+      if (C::FOLD_FROM_TILE_TOP) {
+        ok = advance_stats(j);
+        PK_STAMP(NSWG, j, 7);
+        ok = ok && WARP_ALL(mbar_wait_bounded(bars.pv_done(j % NPV), (j / NPV) & 1, abort_flag, W_DQ_O, kLimit));
+        if (!ok) break;
+        tc_fence_after();
+        PK_STAMP(NSWG, j, 5);
+        tmem_ldN<CH>(o_addr, obuf[0]);
+      }
+      ow = ow_n; c = c_n;
       if (WARP_ANY(ow != 1.f)) {
         const float2 ow2 = make_float2(ow, ow);
 #pragma unroll
@@ -627,16 +644,16 @@ fused_attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
         if (ch == 0) PK_STAMP(NSWG, j, 2);
         if (ch + 1 < NCH) {
           tmem_ldN<CH>(o_addr + (ch + 1) * CH, obuf[(ch + 1) & 1]);
-        } else if (j + 1 < n_tiles && ok) {
+        } else if (!C::FOLD_FROM_TILE_TOP && j + 1 < n_tiles && ok) {
           // first chunk of the next tile (its product was waited for below, chunks ago)
           tmem_ldN<CH>(lane_addr + C::COL_O + ((j + 1) % NO) * D + col0, obuf[(ch + 1) & 1]);
         }
-        if (ch == STAT_AT && j + 1 < n_tiles) {
+        if (!C::FOLD_FROM_TILE_TOP && ch == STAT_AT && j + 1 < n_tiles) {
           PK_STAMP(NSWG, j, 4);
           ok = advance_stats(j + 1);
           PK_STAMP(NSWG, j, 7);
         }
-        if (ch == NEXT_AT && j + 1 < n_tiles) {
+        if (!C::FOLD_FROM_TILE_TOP && ch == NEXT_AT && j + 1 < n_tiles) {
           ok = ok && WARP_ALL(mbar_wait_bounded(bars.pv_done((j + 1) % NPV), ((j + 1) / NPV) & 1, abort_flag, W_DQ_O, kLimit));
           tc_fence_after();
           PK_STAMP(NSWG, j, 5);
