@@ -455,7 +455,8 @@ fused_attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
       };
 
       // Single pass over registers: the whole 64-column tile is loaded once, the score buffer is
-      // re-armed and returned immediately, and t stays in registers between max and exp.
+      // re-armed at once (and handed back after the exponentials), and t stays in registers between
+      // max and exp.
       uint32_t sraw[kKeyTile];
       tmem_ld32(s_addr, sraw);
       tmem_ld32(s_addr + 32, sraw + 32);
@@ -470,9 +471,6 @@ fused_attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
 #pragma unroll
       for (int c2 = 2; c2 < kKeyTile / 2; c2 += 2) { bm0 = max3(bm0, t2[c2].x, t2[c2].y); bm1 = max3(bm1, t2[c2 + 1].x, t2[c2 + 1].y); }
       const float bm = fmaxf(bm0, bm1);
-      tmem_wait_st();
-      tc_fence_before();
-      mbar_arrive(bars.s_free(j % NS));
       PK_STAMP(wg, j, 2);
       float shift, ow = 1.f;
       if (ALGO == kPiper) {
@@ -522,6 +520,12 @@ fused_attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
         }
       }
       PK_STAMP(wg, j, 5);
+      // The score buffer goes back to the S issue warp only now (its arming stores have long
+      // landed, so the wait costs nothing; the S products run two tiles ahead anyway): handing it
+      // back right after the maximum put a tensor-memory wait into the middle of the arithmetic.
+      tmem_wait_st();
+      tc_fence_before();
+      mbar_arrive(bars.s_free(j % NS));
       // probability buffer j%NP was last read by the PV product of tile j-NP
       if (j >= NP && !WARP_ALL(mbar_wait_bounded(bars.pv_done((j - NP) % NPV), ((j - NP) / NPV) & 1, abort_flag, W_SM_PV, kLimit))) break;
       tc_fence_after();
