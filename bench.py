@@ -339,6 +339,26 @@ def library_peaks(dev):
     return out
 
 
+def library_attention(dev, q, k, v, causal, steps=3):
+    """The vendor library's 16-bit attention (torch SDPA, whichever fused backend torch picks) on the
+    same tensors: a comparison row like the reference benchmark's SDPA provider
+    (benchmarks/lib/attention_providers.py), measured outside every timed region and never part of
+    the path under test.  Returns milliseconds per call, or an error string."""
+    import torch
+    import torch.nn.functional as F
+    try:
+        fn = lambda: F.scaled_dot_product_attention(q, k, v, is_causal=causal)  # noqa: E731
+        fn(); torch.cuda.synchronize(dev)
+        ts = []
+        for _ in range(steps):
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record(); fn(); b.record(); torch.cuda.synchronize(dev)
+            ts.append(a.elapsed_time(b))
+        return sorted(ts)[len(ts) // 2]
+    except Exception as exc:  # noqa: BLE001 - a yardstick must not fail the run
+        return f"{type(exc).__name__}: {exc}"[:120]
+
+
 def quality_metrics(actual, reference):
     """Metric definitions of the reference's benchmarks (benchmarks/lib/quality.py:107-180):
     finite pairs only, float64 accumulation."""
@@ -551,6 +571,14 @@ def ours_arm(args, w, rank, local_rank, world):
         for key in ("int8_error", "fp8_error"):
             if key in lib:
                 roofline[key] = lib[key]
+    sdpa = None
+    if not args.no_peaks:
+        t = library_attention(dev, q, k, v, w.causal)
+        sdpa = {"provider": f"torch SDPA, {str(w.dtype).split('.')[-1]} (library kernel, comparison row only)"}
+        if isinstance(t, float):
+            sdpa.update(ms_per_step=t, value=metric_ops(w, local_heads) / (t * 1e-3) / 1e12, unit=UNIT)
+        else:
+            sdpa["error"] = t
     # The prepass is byte work bound by HBM: 2 bytes read + 1 byte written per input element of
     # q, k and v (the second read of K/V for "statistics, then quantise" should hit L2), plus the
     # per-key vectors; the whole prepass (all its launches) is timed as one unit.
@@ -581,6 +609,7 @@ def ours_arm(args, w, rank, local_rank, world):
         "data": "synthetic", "config": workload_config(w, world, args.scaling, heads_per_rank), "clocks": clocks, "e2e": e2e,
         "gpu_launches": (prepass_launches + 1 + (1 if key_split else 0)) * args.steps, "roofline": roofline, "cpu_baseline": cpu_baseline,
         "roofline_prepass": roofline_prepass, "device_status": status[0],
+        "library_attention": sdpa,
         "graph_replay": None if graph_ms is None else {"ms_per_step": graph_ms, "value": total_ops / (graph_ms * 1e-3) / 1e12, "unit": UNIT},
         "per_gpu_value": value / world,
         "value_full_rectangle": (4.0 * total_heads * w.q_len * w.kv_len * w.head_dim / (ms * 1e-3) / 1e12) if w.causal else None,
@@ -608,6 +637,15 @@ def ours_arm(args, w, rank, local_rank, world):
         args.records.parent.mkdir(parents=True, exist_ok=True)
         with args.records.open("a", encoding="utf-8") as f:
             f.write(json.dumps(rec, separators=(",", ":")) + "\n")
+            if sdpa is not None and "ms_per_step" in sdpa:
+                t = sdpa["ms_per_step"]
+                ref_rec = dict(rec, provider="torch_sdpa", quality=None,
+                               configuration={"dtype": str(w.dtype).split(".")[-1], "is_causal": w.causal, "workload": w.name},
+                               timings={"warmup_ms": 0, "measurement_time_ms": max(1, int(3 * t)), "first_call_ms": None,
+                                        "first_call_clock": "synchronized_wall", "preparation": None, "prepared_execution": None,
+                                        "operator_end_to_end": {"median_ms": t, "p20_ms": t, "p80_ms": t, "clock": "device_event"}},
+                               extra={"effective_tflops_end_to_end": sdpa["value"]})
+                f.write(json.dumps(ref_rec, separators=(",", ":")) + "\n")
     if dist is not None:
         dist.destroy_process_group()
 
