@@ -405,6 +405,9 @@ fused_attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
     const float2 neg_magic2 = make_float2(-kMagic, -kMagic);
     uint32_t armv[16];
     load_arm_block(smem_base + C::OFF_MAGIC, armv);
+    // Sage with per-key K scales: t_c = q_mul * (score_c * k_mul_c), nothing added but -inf on
+    // padding, so the row factor can wait until the shift in front of the exponential.
+    constexpr bool ROW_SCALE_LATE = ALGO == kSage && !K_PER_BLOCK;
     for (int j = wg; j < n_tiles; j += NSWG) {
       PK_STAMP(wg, j, 0);
       // votes keep the warp converged for the .sync.aligned tensor-memory ops even when a wait is abandoned
@@ -439,6 +442,12 @@ fused_attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
           if (K_PER_BLOCK) {
             t2[q4 * 2 + 0] = __ffma2_rn(f0, mt2, make_float2(add.x, add.y));
             t2[q4 * 2 + 1] = __ffma2_rn(f1, mt2, make_float2(add.z, add.w));
+          } else if (ROW_SCALE_LATE) {
+            // u_c = score_c * k_mul_c (+ -inf on padding); the positive row factor q_mul is applied
+            // with the shift in front of the exponential, one multiplication per pair fewer
+            const float4 mul = vk[ch * 4 + q4];
+            t2[q4 * 2 + 0] = __ffma2_rn(f0, make_float2(mul.x, mul.y), make_float2(add.x, add.y));
+            t2[q4 * 2 + 1] = __ffma2_rn(f1, make_float2(mul.z, mul.w), make_float2(add.z, add.w));
           } else {
             const float4 mul = vk[ch * 4 + q4];
             t2[q4 * 2 + 0] = __ffma2_rn(__fmul2_rn(f0, mt2), make_float2(mul.x, mul.y), make_float2(add.x, add.y));
@@ -470,7 +479,8 @@ fused_attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
       float bm0 = fmaxf(t2[0].x, t2[0].y), bm1 = fmaxf(t2[1].x, t2[1].y);
 #pragma unroll
       for (int c2 = 2; c2 < kKeyTile / 2; c2 += 2) { bm0 = max3(bm0, t2[c2].x, t2[c2].y); bm1 = max3(bm1, t2[c2 + 1].x, t2[c2 + 1].y); }
-      const float bm = fmaxf(bm0, bm1);
+      // ROW_SCALE_LATE: the maximum was taken over u; q_mul > 0 commutes with it
+      const float bm = ROW_SCALE_LATE ? fmaxf(bm0, bm1) * mt : fmaxf(bm0, bm1);
       PK_STAMP(wg, j, 2);
       float shift, ow = 1.f;
       if (ALGO == kPiper) {
@@ -500,7 +510,8 @@ fused_attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
       uint32_t packed[kKeyTile / 4];
 #pragma unroll
       for (int c4 = 0; c4 < kKeyTile / 4; ++c4) {
-        const float2 d0 = __fadd2_rn(t2[c4 * 2 + 0], shift2), d1 = __fadd2_rn(t2[c4 * 2 + 1], shift2);
+        const float2 d0 = ROW_SCALE_LATE ? __ffma2_rn(t2[c4 * 2 + 0], mt2, shift2) : __fadd2_rn(t2[c4 * 2 + 0], shift2);
+        const float2 d1 = ROW_SCALE_LATE ? __ffma2_rn(t2[c4 * 2 + 1], mt2, shift2) : __fadd2_rn(t2[c4 * 2 + 1], shift2);
         const float2 e0 = make_float2(ex2_approx(d0.x), ex2_approx(d0.y));
         const float2 e1 = make_float2(ex2_approx(d1.x), ex2_approx(d1.y));
         if (ALGO == kPiper) {
