@@ -722,38 +722,66 @@ fused_attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
       for (int d0 = 0; d0 < DH; d0 += 4)
         *reinterpret_cast<float4*>(pr + d0) = make_float4(num2[d0 / 2].x, num2[d0 / 2].y, num2[d0 / 2 + 1].x, num2[d0 / 2 + 1].y);
       *reinterpret_cast<float4*>(pr + DH) = make_float4(mx, ok ? den : bad, 0.f, 0.f);
-    } else if (ok && grow < prm.Sq) {
-      // one IEEE division per row; the D per-element divisions of the reference become
-      // multiplications by the reciprocal (at most an ulp apart, and far less code)
-      const float dinv = __fdiv_rn(1.f, fmaxf(den, 1e-30f));
-      const float* aux = prm.v_aux + static_cast<long long>(bh) * D + col0;
-      const long long obase = (static_cast<long long>(bh) * prm.Sq + grow) * D + col0;
+    } else {
+      // Each thread holds one output row.  Stored from here, a warp's store instruction would touch
+      // 32 rows with 16 bytes each (that epilogue took 6 us per CTA, 11 % of a 64-key-tile CTA).
+      // The rows go through shared memory instead (the K/V rings are idle by now: every product
+      // has completed), padded by 16 bytes so that the 8 lanes of a store phase hit different
+      // banks, and leave as whole rows: 32 lanes x 16 bytes of consecutive addresses.
+      static_assert(C::NDQ == 1, "the staging area is laid out for one dequant warpgroup");
+      static_assert(4 * 32 * (D * 4 + 16) <= NK * C::K_BYTES + NV * C::V_BYTES, "staging fits into the K/V rings");
+      const int esz = (prm.out_dtype == PK_F32) ? 4 : 2;
+      const int row_bytes = D * esz, stride = row_bytes + 16;
+      uint8_t* stage = smem + C::OFF_K + (warp & 3) * 32 * (D * 4 + 16);
+      if (ok && grow < prm.Sq) {
+        // one IEEE division per row; the D per-element divisions of the reference become
+        // multiplications by the reciprocal (at most an ulp apart, and far less code)
+        const float dinv = __fdiv_rn(1.f, fmaxf(den, 1e-30f));
+        const float4* aux4 = reinterpret_cast<const float4*>(prm.v_aux + static_cast<long long>(bh) * D);
+        uint8_t* mine = stage + lane * stride;
 #pragma unroll
-      for (int d0 = 0; d0 < DH; d0 += 8) {
-        float r[8];
+        for (int d0 = 0; d0 < D; d0 += 8) {
+          const float4 a0 = __ldg(aux4 + d0 / 4), a1 = __ldg(aux4 + d0 / 4 + 1);
+          const float aux[8] = {a0.x, a0.y, a0.z, a0.w, a1.x, a1.y, a1.z, a1.w};
+          float r[8];
 #pragma unroll
-        for (int i = 0; i < 8; ++i) {
-          const float nv = (i & 1) ? num2[(d0 + i) / 2].y : num2[(d0 + i) / 2].x;
-          if (ALGO == kPiper) r[i] = fmaf(nv, dinv, aux[d0 + i]);
-          else r[i] = nv * (aux[d0 + i] * (1.f / 448.f)) * dinv;
-        }
-        if (prm.out_dtype == PK_F32) {
-          float4* o = reinterpret_cast<float4*>(static_cast<float*>(prm.out) + obase + d0);
-          o[0] = make_float4(r[0], r[1], r[2], r[3]);
-          o[1] = make_float4(r[4], r[5], r[6], r[7]);
-        } else {
-          uint32_t w[4];
-#pragma unroll
-          for (int i = 0; i < 4; ++i) {
-            if (prm.out_dtype == PK_F16) {
-              const __half2 h = __floats2half2_rn(r[2 * i], r[2 * i + 1]);
-              w[i] = *reinterpret_cast<const uint32_t*>(&h);
-            } else {
-              const __nv_bfloat162 h = __floats2bfloat162_rn(r[2 * i], r[2 * i + 1]);
-              w[i] = *reinterpret_cast<const uint32_t*>(&h);
-            }
+          for (int i = 0; i < 8; ++i) {
+            const float nv = (i & 1) ? num2[(d0 + i) / 2].y : num2[(d0 + i) / 2].x;
+            if (ALGO == kPiper) r[i] = fmaf(nv, dinv, aux[i]);
+            else r[i] = nv * (aux[i] * (1.f / 448.f)) * dinv;
           }
-          *reinterpret_cast<uint4*>(static_cast<uint16_t*>(prm.out) + obase + d0) = make_uint4(w[0], w[1], w[2], w[3]);
+          if (prm.out_dtype == PK_F32) {
+            float4* o = reinterpret_cast<float4*>(mine + d0 * 4);
+            o[0] = make_float4(r[0], r[1], r[2], r[3]);
+            o[1] = make_float4(r[4], r[5], r[6], r[7]);
+          } else {
+            uint32_t pk4[4];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+              if (prm.out_dtype == PK_F16) {
+                const __half2 h = __floats2half2_rn(r[2 * i], r[2 * i + 1]);
+                pk4[i] = *reinterpret_cast<const uint32_t*>(&h);
+              } else {
+                const __nv_bfloat162 h = __floats2bfloat162_rn(r[2 * i], r[2 * i + 1]);
+                pk4[i] = *reinterpret_cast<const uint32_t*>(&h);
+              }
+            }
+            *reinterpret_cast<uint4*>(mine + d0 * 2) = make_uint4(pk4[0], pk4[1], pk4[2], pk4[3]);
+          }
+        }
+      }
+      __syncwarp();
+      if (ok) {  // uniform within the warp (every wait result is voted on)
+        const int lanes_per_row = row_bytes / 16, rows_per_store = 32 / lanes_per_row;
+        const int sub = lane / lanes_per_row, piece = lane % lanes_per_row;
+        const int first_row = q0 + (warp & 3) * 32;
+        uint8_t* out_bytes = static_cast<uint8_t*>(prm.out);
+        for (int it = 0; it < 32 / rows_per_store; ++it) {
+          const int rl = it * rows_per_store + sub;
+          if (first_row + rl < prm.Sq) {
+            const uint4 val = *reinterpret_cast<const uint4*>(stage + rl * stride + piece * 16);
+            *reinterpret_cast<uint4*>(out_bytes + (static_cast<long long>(bh) * prm.Sq + first_row + rl) * row_bytes + piece * 16) = val;
+          }
         }
       }
     }
