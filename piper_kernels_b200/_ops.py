@@ -85,8 +85,9 @@ def _run(algo: str, query, key, value, scale, is_causal, center_value, sort_valu
         p.workspace, p.workspace_bytes = ws.data_ptr(), ws.numel()
         fn = _cabi.lib().pk_piper_attention_fwd if algo == "piper" else _cabi.lib().pk_sage2pp_attention_fwd
         _cabi.check(fn(C.byref(p)))
-        # the kernels run asynchronously on the current stream; keep the scratch alive until then
-        ws.record_stream(torch.cuda.current_stream(query.device))
+        # The kernels run asynchronously on the current stream.  The scratch was allocated on that
+        # stream, so the caching allocator only hands it to work queued behind them: no
+        # record_stream (and its events) needed.
     return out
 
 
