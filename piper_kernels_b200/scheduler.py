@@ -172,18 +172,30 @@ class HostAttentionPipeline:
             start += n
             slot = slots[i % self.n_slots]
             call = self._call(op, i % self.n_slots, n, kwargs)
+            # Nothing hides the first chunk's upload: its K and V go first and their half of the
+            # prepass (means, key order, codes) runs while its Q is still on the way.
+            split_first = i == 0 and not copy_only
             with torch.cuda.stream(self.up):
                 if slot["free"] is not None:
                     self.up.wait_event(slot["free"])  # the fused kernel that read this slot has finished
-                slot["q"][:n].copy_(fq[sl], non_blocking=True)
                 slot["k"][:n].copy_(fk[sl], non_blocking=True)
                 slot["v"][:n].copy_(fv[sl], non_blocking=True)
+                kv_uploaded = torch.cuda.Event()
+                if split_first:
+                    kv_uploaded.record(self.up)
+                slot["q"][:n].copy_(fq[sl], non_blocking=True)
                 uploaded = torch.cuda.Event()
                 uploaded.record(self.up)
             with torch.cuda.stream(self.prep):
-                self.prep.wait_event(uploaded)
-                if not copy_only:
-                    call.prepare()
+                if split_first:
+                    self.prep.wait_event(kv_uploaded)
+                    call.prepare_kv()
+                    self.prep.wait_event(uploaded)
+                    call.requantize_q()
+                else:
+                    self.prep.wait_event(uploaded)
+                    if not copy_only:
+                        call.prepare()
                 prepared = torch.cuda.Event()
                 prepared.record(self.prep)
             run = main if i % 2 == 0 else self.run_b
