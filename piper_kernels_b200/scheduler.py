@@ -75,14 +75,14 @@ def plan_chunks(flat_heads: int, max_chunk: int) -> list[int]:
     return plan
 
 
-def suggest_heads_per_chunk(ops_per_head: float, flat_heads: int, *, target_ms: float = 1.2, tops: float = 800.0,
+def suggest_heads_per_chunk(ops_per_head: float, flat_heads: int, *, target_ms: float = 0.6, tops: float = 800.0,
                             largest: int = 8) -> int:
-    """Chunk size for :class:`HostAttentionPipeline`: enough heads for about a millisecond of
-    fused-kernel time (shorter chunks are bound by their dozen launches, longer ones expose the
-    first upload and the last download), at most ``largest`` and at most a quarter of the heads.
-    ``ops_per_head`` is 4 * q_len * kv_len * head_dim (halved for causal attention).  Measured
-    per step: c4 (0.67 ms per head) 29.0 ms with 2 heads, 29.4 with 4, 32.5 with 8; c5 (0.04 ms per
-    head) 11.8 ms with 4 heads, 13.2 with 2."""
+    """Chunk size for :class:`HostAttentionPipeline`: enough heads for about half a millisecond of
+    fused-kernel time (shorter chunks are bound by their dozen launches, longer ones expose more of
+    the first upload and the last download and leave larger partial waves), at most ``largest`` and
+    at most a quarter of the heads.  ``ops_per_head`` is 4 * q_len * kv_len * head_dim (halved for
+    causal attention).  Measured per step: c4 (0.67 ms per head) 26.8 ms with 1 head, 27.0 with 2,
+    27.2 with 3; c5 (0.04 ms per head) 11.8 ms with 4 heads, 13.2 with 2."""
     per_head_ms = float(ops_per_head) / (tops * 1e9)
     want = int(-(-target_ms // max(per_head_ms, 1e-6)))
     return max(1, min(int(largest), int(flat_heads) // 4, want))
@@ -104,13 +104,13 @@ class HostAttentionPipeline:
     ``sage_attention_2pp``; keyword arguments are the ones that function takes.
     """
 
-    def __init__(self, device, *, heads_per_chunk: int = 2, slots: int = 4):
+    def __init__(self, device, *, heads_per_chunk: int = 1, slots: int = 4, prepass_priority: int = -1):
         self.device = torch.device(device)
         self.heads_per_chunk = int(heads_per_chunk)
         self.n_slots = max(2, int(slots))  # staging slots: uploads run this many chunks ahead of the fused kernels
         self.up = torch.cuda.Stream(self.device)
         self.down = torch.cuda.Stream(self.device)
-        self.prep = torch.cuda.Stream(self.device, priority=-1)
+        self.prep = torch.cuda.Stream(self.device, priority=int(prepass_priority))
         self.run_b = torch.cuda.Stream(self.device)
         self._slots = None
         self._key = None
@@ -218,6 +218,6 @@ class HostAttentionPipeline:
 
 
 def attention_from_host(op, q_host: torch.Tensor, k_host: torch.Tensor, v_host: torch.Tensor,
-                        out_host: torch.Tensor, device, *, heads_per_chunk: int = 2, slots: int = 4, **kwargs) -> torch.Tensor:
+                        out_host: torch.Tensor, device, *, heads_per_chunk: int = 1, slots: int = 4, **kwargs) -> torch.Tensor:
     """One-shot form of :class:`HostAttentionPipeline` (allocates the staging buffers per call)."""
     return HostAttentionPipeline(device, heads_per_chunk=heads_per_chunk, slots=slots)(op, q_host, k_host, v_host, out_host, **kwargs)
