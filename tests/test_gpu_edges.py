@@ -322,3 +322,38 @@ def test_stalled_wait_gives_up_reports_and_leaves_the_device_usable():
     torch.cuda.synchronize()
     assert torch.equal(again, want)
     assert AttentionCall("sage2pp", q, k, v, 128 ** -0.5, False).fwd().status()[0] == 0
+
+
+def test_bench_line_carries_the_contract_keys():
+    """bench.py on the small workload: exactly one JSON line with the keys the benchmark driver
+    and the reviewers read (metric, value, clocks, end-to-end object with its copy sizes, launch
+    count, roofline objects, CPU reference, device status)."""
+    import json
+    import subprocess
+    import sys
+    from pathlib import Path
+
+    root = Path(__file__).resolve().parents[1]
+    r = subprocess.run([sys.executable, str(root / "bench.py"), "--workload", "c1", "--steps", "2", "--warmup", "3",
+                        "--cpu-seconds", "1"], capture_output=True, text=True, timeout=900, cwd=root)
+    assert r.returncode == 0, r.stderr[-2000:]
+    lines = [ln for ln in r.stdout.splitlines() if ln.strip()]
+    assert len(lines) == 1
+    d = json.loads(lines[0])
+    assert d["metric"] == "attention_tops" and d["unit"] == "TOPS" and d["n_gpus"] == 1 and d["steps"] == 2
+    assert d["warmup"] >= 3 and d["higher_is_better"] is True and d["scaling"] == "weak" and d["vs_baseline"] is None
+    assert d["value"] > 0 and d["ms_per_step"] > 0 and d["dtype"] == "int8" and d["data"] == "synthetic"
+    assert d["config"]["workload"].startswith("c1") and "model" not in d["config"]
+    assert d["device_status"] == 0 and d["gpu_launches"] > 0
+    e = d["e2e"]
+    assert e["value"] > 0 and e["h2d_bytes_per_step"] == 3 * 8 * 1024 * 64 * 2 and e["d2h_bytes_per_step"] == 8 * 1024 * 64 * 2
+    assert e["value"] < d["value"]  # host copies inside the timed region
+    rf = d["roofline"]
+    assert rf["bound"] == "tensor" and 0 < rf["frac"] < 1.2 and abs(rf["frac"] - rf["achieved"] / rf["peak"]) < 1e-9
+    rp = d["roofline_prepass"]
+    assert rp["bound"] == "hbm" and 0 < rp["frac"] < 1.2 and rp["unit"] == "GB/s"
+    cb = d["cpu_baseline"]
+    assert cb["kind"] in ("reference", "port") and cb["cores"] >= 1 and cb["value"] > 0 and cb["sample"]
+    ck = d["clocks"]
+    assert ck["sm_mhz"] > 0 and ck["sm_max_mhz"] >= ck["sm_mhz"] and isinstance(ck["reasons"], list)
+    assert d["graph_replay"]["ms_per_step"] > 0 and d["library_attention"]["provider"].startswith("torch SDPA")
