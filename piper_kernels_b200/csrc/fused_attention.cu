@@ -134,7 +134,8 @@ struct Cfg {
   static constexpr int NUM_BARS = 1 + 2 * NK + NV + NVEC + NS + NP + NPV + NO + NSTAT + NM;
   static constexpr int OFF_MISC = (OFF_BAR + NUM_BARS * 8 + 15) / 16 * 16;
   static constexpr int OFF_MAGIC = OFF_MISC + 16;           // 16 words holding the arming pattern
-  static constexpr int SMEM_BYTES = OFF_MAGIC + 64 + 1024;  // + slack for 1024-byte alignment
+  static constexpr int OFF_AUX = OFF_MAGIC + 64;            // head_dim floats: V mean (piper) / V channel scale (sage)
+  static constexpr int SMEM_BYTES = OFF_AUX + D * 4 + 1024;  // + slack for 1024-byte alignment
   static constexpr uint32_t COL_S = 0;
   static constexpr uint32_t COL_P = NS * kKeyTile;
   static constexpr uint32_t COL_O = COL_P + NP * (kKeyTile / 4);
@@ -575,6 +576,11 @@ fused_attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
     tc_fence_before();
     for (int i = 0; i < NO; ++i) mbar_arrive(bars.o_empty(i));
 
+    // The epilogue adds the V mean (multiplies by the V scale) of every column: fetched now, one
+    // float per thread, so that its trip to L2 is over long before the values are needed.
+    float* aux_s = reinterpret_cast<float*>(smem + C::OFF_AUX);
+    if (row < D) aux_s[row] = prm.v_aux[static_cast<long long>(bh) * D + row];
+
     float2 num2[DH / 2];
 #pragma unroll
     for (int d = 0; d < DH / 2; ++d) num2[d] = make_float2(0.f, 0.f);
@@ -730,6 +736,7 @@ fused_attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
       // banks, and leave as whole rows: 32 lanes x 16 bytes of consecutive addresses.
       static_assert(C::NDQ == 1, "the staging area is laid out for one dequant warpgroup");
       static_assert(4 * 32 * (D * 4 + 16) <= NK * C::K_BYTES + NV * C::V_BYTES, "staging fits into the K/V rings");
+      asm volatile("bar.sync 1, 128;" ::: "memory");  // the dequant warpgroup's aux_s writes, made before its main loop
       const int esz = (prm.out_dtype == PK_F32) ? 4 : 2;
       const int row_bytes = D * esz, stride = row_bytes + 16;
       uint8_t* stage = smem + C::OFF_K + (warp & 3) * 32 * (D * 4 + 16);
@@ -737,11 +744,11 @@ fused_attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
         // one IEEE division per row; the D per-element divisions of the reference become
         // multiplications by the reciprocal (at most an ulp apart, and far less code)
         const float dinv = __fdiv_rn(1.f, fmaxf(den, 1e-30f));
-        const float4* aux4 = reinterpret_cast<const float4*>(prm.v_aux + static_cast<long long>(bh) * D);
+        const float4* aux4 = reinterpret_cast<const float4*>(aux_s);
         uint8_t* mine = stage + lane * stride;
 #pragma unroll
         for (int d0 = 0; d0 < D; d0 += 8) {
-          const float4 a0 = __ldg(aux4 + d0 / 4), a1 = __ldg(aux4 + d0 / 4 + 1);
+          const float4 a0 = aux4[d0 / 4], a1 = aux4[d0 / 4 + 1];
           const float aux[8] = {a0.x, a0.y, a0.z, a0.w, a1.x, a1.y, a1.z, a1.w};
           float r[8];
 #pragma unroll
