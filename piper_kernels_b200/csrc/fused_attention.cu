@@ -70,6 +70,7 @@ constexpr int NO = 2;      // PV partial buffers in tensor memory
 constexpr int NPV = NV;    // completion barriers of the PV products: one per V stage (a multiple of NP)
 constexpr int VEC_FLOATS = 3 * kKeyTile;
 constexpr uint32_t TMEM_COLS = 512;
+constexpr int kPrefetchCtasAhead = 160;  // a little more than one CTA per SM
 constexpr float kMagic = 12582912.f;    // 1.5 * 2^23: adding it rounds to an integer (ties to even)
 constexpr uint32_t kMagicBits = 0x4B400000u;  // bit pattern of kMagic
 
@@ -289,6 +290,15 @@ fused_attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
     if (HELECT) {
       mbar_expect_tx(bars.q_full(), C::Q_BYTES);
       tma_load_2d(smem_base + C::OFF_Q, &tm_q, bars.q_full(), 0, bh * prm.sq_pad + q0);
+      // A Q tile is read once, from DRAM, and nothing of its CTA can start before it has arrived:
+      // the tile of the CTA about one wave further on (the one that will follow on some SM when
+      // the current wave retires) is brought into L2 now.
+      const long long next = static_cast<long long>(bh) * gridDim.x + blockIdx.x + kPrefetchCtasAhead;
+      if (blockIdx.z == 0 && next < static_cast<long long>(gridDim.x) * gridDim.y) {
+        const int nbh = static_cast<int>(next / gridDim.x), nx = static_cast<int>(next % gridDim.x);
+        const int nqt = causal ? (n_qt - 1 - nx) : nx;
+        tma_prefetch_l2_2d(&tm_q, 0, nbh * prm.sq_pad + nqt * kQTile);
+      }
     }
     const long long vec_base = static_cast<long long>(bh) * prm.sk_pad;
     int last = -1;  // last key tile whose copies were issued
