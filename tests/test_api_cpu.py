@@ -187,3 +187,36 @@ def test_chunk_size_follows_the_work_per_head():
     assert got == {"c1": 2, "c2": 8, "c3": 8, "c4": 1, "c5": 8}
     assert suggest_heads_per_chunk(WORKLOADS["c4"].ops(1), 5) == 1  # a strong-scaling shard of five heads
     assert suggest_heads_per_chunk(1e15, 64) == 1 and suggest_heads_per_chunk(1.0, 3) == 1
+
+
+def test_magic_number_rounding_equals_rint_and_yields_the_code_byte():
+    """The arithmetic the quantisers use for an INT8 code, restated in numpy: adding 1.5 * 2^23 to
+    t in FP32 rounds it to an integer like rint (ties to even), and the low byte of the sum's bit
+    pattern is that integer in two's complement.  The guard that sends elements near a
+    half-integer to the exact division is wider than the distance between x * fl(1/s) and x / s."""
+    import numpy as np
+
+    rng = np.random.default_rng(7)
+    t = np.concatenate([
+        rng.uniform(-127.4, 127.4, 200000),
+        np.arange(-127, 127) + 0.5,                       # exact ties
+        np.arange(-127, 127) + 0.5 + 2.0 ** -17,          # just above a tie
+        np.arange(-127, 127) + 0.5 - 2.0 ** -17,
+        [0.0, -0.0, 127.0, -127.0, 126.5, -126.5],
+    ]).astype(np.float32)
+    magic = np.float32(12582912.0)
+    tm = (t + magic).astype(np.float32)
+    q = (tm - magic).astype(np.float32)
+    assert np.array_equal(q, np.rint(t))
+    code = (tm.view(np.uint32) & 0xFF).astype(np.uint8).view(np.int8)
+    assert np.array_equal(code.astype(np.float32), np.rint(t))
+    # |x * fl(1/s) - x / s| for |x / s| <= 127: far inside the 1e-4 guard around half-integers
+    x = rng.standard_normal(200000).astype(np.float32) * 3
+    s = (np.abs(x).max() / np.float32(127.0) + np.float32(1e-7)).astype(np.float32)
+    r = (np.float32(1.0) / s).astype(np.float32)
+    gap = np.abs((x * r).astype(np.float32).astype(np.float64) - x.astype(np.float64) / np.float64(s))
+    assert gap.max() < 2.4e-5
+    exact = np.rint((x / s).astype(np.float32))
+    fast = np.rint((x * r).astype(np.float32))
+    near_half = np.abs(np.abs((x * r).astype(np.float32) - fast) - 0.5) < 1e-4
+    assert np.array_equal(fast[~near_half], exact[~near_half])
