@@ -827,6 +827,10 @@ __global__ void __launch_bounds__(256) merge_splits_kernel(const float* __restri
   constexpr int VEC = D / 32;  // columns per lane
   const long long gw = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
   const int lane = threadIdx.x & 31;
+  // Launched with programmatic stream serialisation: this kernel may start while the fused kernel
+  // is still running (its launch latency hides behind that kernel's tail); the partial rows are
+  // complete and visible once this returns.
+  cudaGridDependencySynchronize();
   if (gw >= rows_total) return;
   const long long bh = gw / Sq;
   const int row = static_cast<int>(gw % Sq);
@@ -942,8 +946,23 @@ int launch_one_impl(const pk_problem& p, const Layout& L, cudaStream_t st, const
   if (splits > 1) {
     const long long rows = static_cast<long long>(L.BH) * L.Sq;
     const unsigned blocks = static_cast<unsigned>((rows * 32 + 255) / 256);
-    merge_splits_kernel<D, ALGO><<<blocks, 256, 0, st>>>(prm.partial, prm.v_aux, p.out, p.out_dtype, L.Sq, L.sq_pad, splits, rows);
-    e = cudaGetLastError();
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = dim3(blocks);
+    cfg.blockDim = dim3(256);
+    cfg.dynamicSmemBytes = 0;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    const float* partial_c = prm.partial;
+    const float* aux_c = prm.v_aux;
+    void* out_c = p.out;
+    int out_dtype_c = p.out_dtype, sq_c = L.Sq, sq_pad_c = L.sq_pad, splits_c = splits;
+    long long rows_c = rows;
+    e = cudaLaunchKernelEx(&cfg, merge_splits_kernel<D, ALGO>, partial_c, aux_c, out_c, out_dtype_c, sq_c, sq_pad_c, splits_c, rows_c);
+    if (e == cudaSuccess) e = cudaGetLastError();
     if (e != cudaSuccess) return fail(PK_ERR_CUDA, "merge kernel launch failed: %s", cuda_err(e));
   }
   return PK_OK;
