@@ -274,6 +274,9 @@ fused_attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
     tmem_relinquish();
     tc_fence_before();
   }
+  // The kernel is launched chained to its predecessor in the stream (the prepass): everything up to
+  // here touches only this CTA's shared and tensor memory; from here on the prepass's results are read.
+  cudaGridDependencySynchronize();
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
@@ -940,8 +943,8 @@ int launch_one_impl(const pk_problem& p, const Layout& L, cudaStream_t st, const
     }
   }
   const dim3 grid(L.sq_pad / kQTile, L.BH, splits);
-  kern<<<grid, C::THREADS, C::SMEM_BYTES, st>>>(tq, tk, tv, prm);
-  cudaError_t e = cudaGetLastError();
+  cudaError_t e = launch_chained(kern, grid, dim3(C::THREADS), C::SMEM_BYTES, st, tq, tk, tv, prm);
+  if (e == cudaSuccess) e = cudaGetLastError();
   if (e != cudaSuccess) return fail(PK_ERR_CUDA, "fused kernel launch failed: %s", cuda_err(e));
   if (splits > 1) {
     const long long rows = static_cast<long long>(L.BH) * L.Sq;

@@ -2,6 +2,8 @@
 #pragma once
 
 #include <cuda_runtime.h>
+
+#include <utility>
 #include <stddef.h>
 #include <stdint.h>
 
@@ -74,5 +76,28 @@ template <typename T>
 inline T* at(const pk_problem& p, size_t off) {
   return reinterpret_cast<T*>(static_cast<char*>(p.workspace) + off);
 }
+
+#ifdef __CUDACC__
+// Launch with programmatic stream serialisation: the kernel may be set up and start while its
+// predecessor in the stream is still draining, which hides most of the launch latency between the
+// library's back-to-back kernels (a call is eight launches; small problems are bound by them).
+// Every kernel launched this way calls cudaGridDependencySynchronize() before it touches memory:
+// that returns once the predecessor has completed and its writes are visible.
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_chained(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st,
+                                  Args&&... args) {
+  cudaLaunchConfig_t cfg{};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(std::forward<Args>(args))...);
+}
+#endif
 
 }  // namespace pk

@@ -94,6 +94,7 @@ template <typename T, int D, bool ALIGNED>
 __global__ void __launch_bounds__(kThreads) colstat_partial_kernel(
     TensorArg k, TensorArg v, double* __restrict__ k_part, double* __restrict__ v_part, int sk, int heads,
     int chunks, int do_k, int v_mode) {
+  cudaGridDependencySynchronize();  // launched chained: wait for the predecessor's writes
   constexpr int TPR = D / 8;           // threads per row
   constexpr int RPP = kThreads / TPR;  // rows per pass
   __shared__ double red[RPP * D];
@@ -186,6 +187,7 @@ __global__ void colstat_finalize_kernel(const double* __restrict__ k_part, const
                                         const float* __restrict__ k_override, const float* __restrict__ v_override,
                                         float* __restrict__ k_mean, float* __restrict__ v_out, int sk, int D,
                                         int chunks, int v_mode) {
+  cudaGridDependencySynchronize();  // launched chained: wait for the predecessor's writes
   const int bh = blockIdx.x, d = threadIdx.x % D;
   const bool v_role = static_cast<int>(threadIdx.x) >= D;
   const long long base = static_cast<long long>(bh) * chunks * D + d;
@@ -221,6 +223,7 @@ constexpr int kRangePasses = 8;  // row passes per CTA of row_range_kernel
 template <typename T, int D, bool ALIGNED>
 __global__ void __launch_bounds__(kThreads) row_range_kernel(TensorArg v, const float* __restrict__ v_mean,
                                                              uint32_t* __restrict__ keys, int sk, int heads) {
+  cudaGridDependencySynchronize();  // launched chained: wait for the predecessor's writes
   constexpr int TPR = D / 8;
   constexpr int RPP = kThreads / TPR;
   const int bh = blockIdx.y;
@@ -395,6 +398,7 @@ __global__ void __launch_bounds__(kSortThreads) segment_sort_kernel(uint32_t* __
                                                                     uint32_t* __restrict__ keys1,
                                                                     int32_t* __restrict__ idx0,
                                                                     int32_t* __restrict__ idx1, int n) {
+  cudaGridDependencySynchronize();  // launched chained: wait for the predecessor's writes
   segment_sort_body(keys0, keys1, idx0, idx1, n, blockIdx.x);
 }
 
@@ -620,6 +624,7 @@ __global__ void __launch_bounds__(kThreads, 3) quantize_qk_kernel(
     TensorArg x, const float* __restrict__ mean, const int32_t* __restrict__ order, int8_t* __restrict__ codes,
     float* __restrict__ gscale, float* __restrict__ row_mul, int len, int len_pad, int heads, int per_thread,
     int groups_per_head, float mul) {
+  cudaGridDependencySynchronize();  // launched chained: wait for the predecessor's writes
   // two blocks per CTA (eight 16-byte loads in flight per thread) measured 15 % faster than one
   // block with the unpacked values held, most of all for rows gathered through the key order
   __shared__ float row_max[kQuantBlocks * kBlockRows];
@@ -646,6 +651,7 @@ __global__ void __launch_bounds__(kSortThreads) sort_and_quantize_q_kernel(
     int n_keys, int n_heads, TensorArg q, int8_t* __restrict__ codes, float* __restrict__ gscale,
     float* __restrict__ row_mul, int len, int len_pad, int heads, int per_thread, int groups_per_head, float mul,
     int q_ctas_per_head) {
+  cudaGridDependencySynchronize();  // launched chained: wait for the predecessor's writes
   constexpr int GROUPS = kSortThreads / kThreads;
   if (static_cast<int>(blockIdx.x) < n_heads) {
     segment_sort_body(keys0, keys1, idx0, idx1, n_keys, blockIdx.x);
@@ -792,6 +798,7 @@ __global__ void __launch_bounds__(kThreads, 3) quantize_v_kernel(
     TensorArg v, const float* __restrict__ v_mean_or_scale, const int32_t* __restrict__ order,
     uint8_t* __restrict__ codes_t, float* __restrict__ v_scale, float* __restrict__ col_add,
     float* __restrict__ col_inv, int sk, int sk_pad, int heads) {
+  cudaGridDependencySynchronize();  // launched chained: wait for the predecessor's writes
   __shared__ __align__(16) uint32_t tile[D * kQuantBlocks * kBlockRows / 4];
   // every key of this CTA's blocks exists (all CTAs of a head but the last): no per-key checks
   if ((static_cast<int>(blockIdx.x) + 1) * kQuantBlocks * kBlockRows <= sk) {
@@ -802,6 +809,7 @@ __global__ void __launch_bounds__(kThreads, 3) quantize_v_kernel(
 }
 
 __global__ void zero_words_kernel(int32_t* p, int n) {
+  cudaGridDependencySynchronize();  // launched chained: wait for the predecessor's writes
   const int i = blockIdx.x * blockDim.x + threadIdx.x;
   if (i < n) p[i] = 0;
 }
@@ -824,14 +832,13 @@ int run_prepass(const pk_problem& p, const Layout& L, Algo algo, cudaStream_t st
   const bool sort = !sage && p.sort_value_rows;
   const int per_thread = p.qk_granularity == PK_QK_PER_THREAD;
 
-  zero_words_kernel<<<1, 32, 0, st>>>(at<int32_t>(p, L.status), 16);
+  launch_chained(zero_words_kernel, dim3(1), dim3(32), 0, st, at<int32_t>(p, L.status), 16);
   const bool do_kv = (parts & kPrepassKV) != 0, do_q = (parts & kPrepassQ) != 0;
 
   // With a key order to compute, the Q quantisation shares the launch of the sort (below).
   const bool q_with_sort = do_q && do_kv && sort;
   if (do_q && !q_with_sort) {
-    quantize_qk_kernel<T, D, false, ALIGNED><<<dim3(ceil_div(L.sq_pad / kBlockRows, kQuantBlocks), BH), kThreads, 0, st>>>(
-        q, nullptr, nullptr, at<int8_t>(p, L.q_codes), at<float>(p, L.q_gscale), at<float>(p, L.q_mul), L.Sq,
+    launch_chained(quantize_qk_kernel<T, D, false, ALIGNED>, dim3(dim3(ceil_div(L.sq_pad / kBlockRows, kQuantBlocks), BH)), dim3(kThreads), 0, st, q, nullptr, nullptr, at<int8_t>(p, L.q_codes), at<float>(p, L.q_gscale), at<float>(p, L.q_mul), L.Sq,
         L.sq_pad, p.heads, per_thread, L.q_groups, p.scale * kLog2e);
   }
   if (!do_kv) {
@@ -844,13 +851,12 @@ int run_prepass(const pk_problem& p, const Layout& L, Algo algo, cudaStream_t st
   const int do_k = p.k_mean_override == nullptr;
   const int v_mode = sage ? 2 : ((center && p.v_mean_override == nullptr) ? 1 : 0);
   if (do_k || v_mode) {
-    colstat_partial_kernel<T, D, ALIGNED><<<dim3(L.chunks, BH), kThreads, 0, st>>>(
-        k, v, at<double>(p, L.k_part), at<double>(p, L.v_part), L.Sk, p.heads, L.chunks, do_k, v_mode);
+    launch_chained(colstat_partial_kernel<T, D, ALIGNED>, dim3(dim3(L.chunks, BH)), dim3(kThreads), 0, st, k, v, at<double>(p, L.k_part), at<double>(p, L.v_part), L.Sk, p.heads, L.chunks, do_k, v_mode);
   }
   // v slot: piper -> mean [BH,D]; sage -> channel scale [BH,D] (stored in the v_scale view)
   float* v_stat = sage ? at<float>(p, L.v_scale) : at<float>(p, L.v_mean);
   const int fin_mode = sage ? 2 : (center ? 1 : 0);
-  colstat_finalize_kernel<<<BH, 2 * D, 0, st>>>(at<double>(p, L.k_part), at<double>(p, L.v_part), p.k_mean_override,
+  launch_chained(colstat_finalize_kernel, dim3(BH), dim3(2 * D), 0, st, at<double>(p, L.k_part), at<double>(p, L.v_part), p.k_mean_override,
                                             center ? p.v_mean_override : nullptr, at<float>(p, L.k_mean), v_stat,
                                             L.Sk, D, L.chunks, fin_mode);
 
@@ -858,34 +864,29 @@ int run_prepass(const pk_problem& p, const Layout& L, Algo algo, cudaStream_t st
   const int32_t* order = nullptr;
   if (sort) {
     constexpr int RPB = kRangePasses * (kThreads / (D / 8));  // rows per CTA
-    row_range_kernel<T, D, ALIGNED><<<dim3((L.Sk + RPB - 1) / RPB, BH), kThreads, 0, st>>>(
-        v, at<float>(p, L.v_mean), at<uint32_t>(p, L.range), L.Sk, p.heads);
+    launch_chained(row_range_kernel<T, D, ALIGNED>, dim3(dim3((L.Sk + RPB - 1) / RPB, BH)), dim3(kThreads), 0, st, v, at<float>(p, L.v_mean), at<uint32_t>(p, L.range), L.Sk, p.heads);
     if (q_with_sort) {
       const int q_ctas = ceil_div(L.sq_pad / kBlockRows, kSortThreads / kThreads);
-      sort_and_quantize_q_kernel<T, D, ALIGNED><<<BH + BH * q_ctas, kSortThreads, 0, st>>>(
-          at<uint32_t>(p, L.range), at<uint32_t>(p, L.keys_alt), at<int32_t>(p, L.idx_a), at<int32_t>(p, L.idx_b),
+      launch_chained(sort_and_quantize_q_kernel<T, D, ALIGNED>, dim3(BH + BH * q_ctas), dim3(kSortThreads), 0, st, at<uint32_t>(p, L.range), at<uint32_t>(p, L.keys_alt), at<int32_t>(p, L.idx_a), at<int32_t>(p, L.idx_b),
           L.Sk, BH, q, at<int8_t>(p, L.q_codes), at<float>(p, L.q_gscale), at<float>(p, L.q_mul), L.Sq, L.sq_pad,
           p.heads, per_thread, L.q_groups, p.scale * kLog2e, q_ctas);
     } else {
-      segment_sort_kernel<<<BH, kSortThreads, 0, st>>>(at<uint32_t>(p, L.range), at<uint32_t>(p, L.keys_alt),
+      launch_chained(segment_sort_kernel, dim3(BH), dim3(kSortThreads), 0, st, at<uint32_t>(p, L.range), at<uint32_t>(p, L.keys_alt),
                                                        at<int32_t>(p, L.idx_a), at<int32_t>(p, L.idx_b), L.Sk);
     }
     order = at<int32_t>(p, L.idx_a);
   }
 
   // 3. K codes
-  quantize_qk_kernel<T, D, true, ALIGNED><<<dim3(ceil_div(L.sk_pad / kBlockRows, kQuantBlocks), BH), kThreads, 0, st>>>(
-      k, at<float>(p, L.k_mean), order, at<int8_t>(p, L.k_codes), at<float>(p, L.k_gscale), at<float>(p, L.k_mul),
+  launch_chained(quantize_qk_kernel<T, D, true, ALIGNED>, dim3(dim3(ceil_div(L.sk_pad / kBlockRows, kQuantBlocks), BH)), dim3(kThreads), 0, st, k, at<float>(p, L.k_mean), order, at<int8_t>(p, L.k_codes), at<float>(p, L.k_gscale), at<float>(p, L.k_mul),
       L.Sk, L.sk_pad, p.heads, per_thread, L.k_groups, 1.0f);
 
   // 4. V codes
   if (sage) {
-    quantize_v_kernel<T, D, true, ALIGNED><<<dim3(ceil_div(L.sk_pad / kBlockRows, kQuantBlocks), BH), kThreads, 0, st>>>(
-        v, at<float>(p, L.v_scale), nullptr, at<uint8_t>(p, L.v_codes), nullptr, at<float>(p, L.k_add), nullptr,
+    launch_chained(quantize_v_kernel<T, D, true, ALIGNED>, dim3(dim3(ceil_div(L.sk_pad / kBlockRows, kQuantBlocks), BH)), dim3(kThreads), 0, st, v, at<float>(p, L.v_scale), nullptr, at<uint8_t>(p, L.v_codes), nullptr, at<float>(p, L.k_add), nullptr,
         L.Sk, L.sk_pad, p.heads);
   } else {
-    quantize_v_kernel<T, D, false, ALIGNED><<<dim3(ceil_div(L.sk_pad / kBlockRows, kQuantBlocks), BH), kThreads, 0, st>>>(
-        v, at<float>(p, L.v_mean), order, at<uint8_t>(p, L.v_codes), at<float>(p, L.v_scale), at<float>(p, L.k_add),
+    launch_chained(quantize_v_kernel<T, D, false, ALIGNED>, dim3(dim3(ceil_div(L.sk_pad / kBlockRows, kQuantBlocks), BH)), dim3(kThreads), 0, st, v, at<float>(p, L.v_mean), order, at<uint8_t>(p, L.v_codes), at<float>(p, L.v_scale), at<float>(p, L.k_add),
         at<float>(p, L.k_inv), L.Sk, L.sk_pad, p.heads);
   }
   const cudaError_t e = cudaGetLastError();
@@ -955,9 +956,9 @@ void launch_means_static(const pk_problem& p, double* scratch, float* k_mean, fl
   double* v_part = scratch + kStaticPartialsPerTensor;
   const bool al = aligned16(p.k, p.k_stride, 2) && aligned16(p.v, p.v_stride, 2);
   // Each launch overwrites every partial it later reads, so nothing needs clearing first.
-  if (al) colstat_partial_kernel<T, D, true><<<dim3(chunks, BH), kThreads, 0, st>>>(k, v, k_part, v_part, p.kv_len, p.heads, chunks, 1, 1);
-  else colstat_partial_kernel<T, D, false><<<dim3(chunks, BH), kThreads, 0, st>>>(k, v, k_part, v_part, p.kv_len, p.heads, chunks, 1, 1);
-  colstat_finalize_kernel<<<BH, 2 * D, 0, st>>>(k_part, v_part, nullptr, nullptr, k_mean, v_mean, p.kv_len, D, chunks, 1);
+  if (al) launch_chained(colstat_partial_kernel<T, D, true>, dim3(dim3(chunks, BH)), dim3(kThreads), 0, st, k, v, k_part, v_part, p.kv_len, p.heads, chunks, 1, 1);
+  else launch_chained(colstat_partial_kernel<T, D, false>, dim3(dim3(chunks, BH)), dim3(kThreads), 0, st, k, v, k_part, v_part, p.kv_len, p.heads, chunks, 1, 1);
+  launch_chained(colstat_finalize_kernel, dim3(BH), dim3(2 * D), 0, st, k_part, v_part, nullptr, nullptr, k_mean, v_mean, p.kv_len, D, chunks, 1);
 }
 
 }  // namespace
